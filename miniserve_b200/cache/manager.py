@@ -22,7 +22,7 @@ from typing import Sequence
 
 import torch
 
-from ..parts.base import FixedState, PagedKV
+from ..parts.base import FixedState, PagedKV, flat_needs
 from ..parts.decoder import EntryCache
 from .blocks import BlockAllocator, BlockTable, OutOfBlocks
 
@@ -88,12 +88,13 @@ def group_needs(entry_caches: Sequence[EntryCache]) -> tuple[list[tuple[PagedKV,
     groups: dict[PagedKV, int] = {}
     states: list[FixedState] = []
     for i, ec in enumerate(entry_caches):
-        if ec.owner != i or ec.need is None:
+        if ec.owner != i:
             continue
-        if isinstance(ec.need, PagedKV):
-            groups[ec.need] = groups.get(ec.need, 0) + 1
-        elif isinstance(ec.need, FixedState):
-            states.append(ec.need)
+        for need in flat_needs(ec.need):  # a mixer made of several may need pages and state, or several states
+            if isinstance(need, PagedKV):
+                groups[need] = groups.get(need, 0) + 1
+            elif isinstance(need, FixedState):
+                states.append(need)
     return list(groups.items()), states
 
 
@@ -135,43 +136,52 @@ class CacheManager:
         self._entry_view: list[KVEntryView | StateEntryView | None] = []
         self._state_entries: list[tuple[int, FixedState]] = []
         by_need: dict[PagedKV, int] = {}
-        owners: dict[int, tuple[int, int]] = {}  # owner entry -> (group, index in group)
+        owners: dict[tuple[int, int], tuple[int, int]] = {}  # (owner entry, which of its needs) -> (group, index in group)
         for i, ec in enumerate(entry_caches):
             if ec.owner != i or ec.need is None:
                 continue
-            if isinstance(ec.need, PagedKV):
-                g = by_need.get(ec.need)
-                if g is None:
-                    g = len(self.groups)
-                    by_need[ec.need] = g
-                    self.groups.append(CacheGroup(ec.need, [], BlockAllocator(per_group[g], page_size), page_size))
-                owners[i] = (g, len(self.groups[g].entries))
-                self.groups[g].entries.append(i)
-            elif isinstance(ec.need, FixedState):
-                self._state_entries.append((i, ec.need))
-            else:
-                raise TypeError(f"run entry {i} asks for an unknown kind of cache: {ec.need!r}")
+            for n, need in enumerate(flat_needs(ec.need)):
+                if isinstance(need, PagedKV):
+                    g = by_need.get(need)
+                    if g is None:
+                        g = len(self.groups)
+                        by_need[need] = g
+                        self.groups.append(CacheGroup(need, [], BlockAllocator(per_group[g], page_size), page_size))
+                    owners[(i, n)] = (g, len(self.groups[g].entries))
+                    self.groups[g].entries.append(i)
+                elif isinstance(need, FixedState):
+                    self._state_entries.append(((i, n), need))
+                else:
+                    raise TypeError(f"run entry {i} asks for an unknown kind of cache: {need!r}")
         if self.device is not None:
             for grp in self.groups:
                 shape = (len(grp.entries), grp.allocator.num_blocks + 1, grp.need.kv_heads, page_size, grp.need.head_dim)
                 fill = float("nan") if poison else 0.0
                 grp.k = torch.full(shape, fill, dtype=dtype, device=self.device)
                 grp.v = torch.full(shape, fill, dtype=dtype, device=self.device)
-        state_tensors: dict[int, torch.Tensor | None] = {}
+        state_tensors: dict[tuple[int, int], torch.Tensor | None] = {}
         for i, need in self._state_entries:
             # one slot more than there are requests: the padding rows of a captured graph read and write it
             state_tensors[i] = (torch.zeros((max_requests + 1, *need.shape), dtype=need.dtype, device=self.device)
                                 if self.device is not None else None)
-        for i, ec in enumerate(entry_caches):
-            if ec.need is None:
-                self._entry_view.append(None)
-            elif isinstance(ec.need, PagedKV):
-                g, idx = owners[ec.owner]
+        def view(owner: int, need, count: list):
+            """The view of one need, or a tuple of views shaped like a tuple of needs."""
+            if need is None:
+                return None
+            if not isinstance(need, (PagedKV, FixedState)):
+                return tuple(view(owner, part, count) for part in need)
+            n = count[0]
+            count[0] += 1
+            if isinstance(need, PagedKV):
+                g, idx = owners[(owner, n)]
                 grp = self.groups[g]
-                self._entry_view.append(KVEntryView(g, grp.k[idx] if grp.k is not None else None,
-                                                    grp.v[idx] if grp.v is not None else None, page_size))
-            else:
-                self._entry_view.append(StateEntryView(state_tensors[ec.owner], tuple(ec.need.shape)))
+                return KVEntryView(g, grp.k[idx] if grp.k is not None else None, grp.v[idx] if grp.v is not None else None,
+                                   page_size)
+            return StateEntryView(state_tensors[(owner, n)], tuple(need.shape))
+
+        for ec in entry_caches:
+            self._entry_view.append(view(ec.owner, ec.need, [0]))
+        self._state_views = [v for v in self._flat_views() if isinstance(v, StateEntryView)]
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self._live: set[int] = set()
 
@@ -198,8 +208,27 @@ class CacheManager:
 
     def state_bytes(self) -> int:
         """Bytes of the per-request state tensors (one slot per request the cache can hold)."""
-        return sum(v.state.numel() * v.state.element_size() for v in self._entry_view
-                   if isinstance(v, StateEntryView) and v.state is not None)
+        seen = {id(v.state): v.state for v in self._state_views if v.state is not None}
+        return sum(t.numel() * t.element_size() for t in seen.values())
+
+    def _flat_views(self) -> list:
+        out: list = []
+
+        def walk(v):
+            if isinstance(v, tuple):
+                for part in v:
+                    walk(part)
+            elif v is not None:
+                out.append(v)
+
+        for v in self._entry_view:
+            walk(v)
+        return out
+
+    def state_tensors(self) -> list[torch.Tensor]:
+        """Every per-request state tensor once (slot-indexed along the first axis)."""
+        seen = {id(v.state): v.state for v in self._state_views if v.state is not None}
+        return list(seen.values())
 
     # ------------------------------------------------------------------ requests
     def new_request(self) -> RequestCache:

@@ -21,6 +21,9 @@ class Architecture:
     name: str
     parse_config: Callable[[Mapping[str, Any]], Any]  # raw config.json dict -> typed configuration
     model_spec: Callable[[Any], ModelSpec]  # typed configuration -> what the model is made of
+    # Sizes that config.json leaves to the checkpoint: (raw config, {tensor name: shape}) -> raw config with
+    # them filled in. None: config.json says everything.
+    complete: Callable[[Mapping[str, Any], Mapping[str, tuple]], Mapping[str, Any]] | None = None
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
@@ -42,7 +45,7 @@ def architectures() -> list[str]:
 
 
 def architecture_of(raw: Mapping[str, Any]) -> Architecture:
-    names = raw.get("architectures")
+    names = raw.get("architectures") or ([raw["architecture"]] if raw.get("architecture") else None)
     if not names:
         raise ValueError("config.json has no 'architectures' entry; cannot choose a model class")
     name = names[0]
@@ -59,8 +62,25 @@ def load_config_dict(model_dir: str | Path) -> dict[str, Any]:
     return json.loads(path.read_text())
 
 
-def resolve(raw: Mapping[str, Any]) -> tuple[Architecture, Any, ModelSpec]:
-    """(architecture, typed configuration, model spec) for a raw config.json dict."""
+def checkpoint_shapes(model_dir: str | Path) -> dict[str, tuple[int, ...]]:
+    """{tensor name: shape} of every safetensors file of a folder, from the files' headers alone (eight
+    bytes of little-endian length, then that many bytes of JSON)."""
+    import struct
+
+    out: dict[str, tuple[int, ...]] = {}
+    for f in sorted(Path(model_dir).glob("*.safetensors")):
+        with open(f, "rb") as fh:
+            (n,) = struct.unpack("<Q", fh.read(8))
+            header = json.loads(fh.read(n))
+        out.update({k: tuple(v["shape"]) for k, v in header.items() if k != "__metadata__"})
+    return out
+
+
+def resolve(raw: Mapping[str, Any], model_dir: str | Path | None = None) -> tuple[Architecture, Any, ModelSpec]:
+    """(architecture, typed configuration, model spec) for a raw config.json dict. ``model_dir``: where
+    the checkpoint is, for architectures that take some sizes from the tensors' shapes."""
     arch = architecture_of(raw)
+    if arch.complete is not None and model_dir is not None:
+        raw = arch.complete(raw, checkpoint_shapes(model_dir))
     cfg = arch.parse_config(raw)
     return arch, cfg, arch.model_spec(cfg)

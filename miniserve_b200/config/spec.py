@@ -40,7 +40,7 @@ class LayerSpec:
     prefix: str
     block: PartSpec
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None  # None: the layer has a mixer only (and no second norm)
     norms: Mapping[str, PartSpec]
 
     def __post_init__(self):

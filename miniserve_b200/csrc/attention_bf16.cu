@@ -104,7 +104,7 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
                     const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
                     const int* __restrict__ cu_q, const int* __restrict__ q_start, const int* __restrict__ page_indptr,
                     const int* __restrict__ page_indices, int nq, int nkv, float scale_log2, int window,
-                    int page_shift) {
+                    int sink, int page_shift) {
   pdl_prologue();
   const int r = blockIdx.y, head = blockIdx.z;
   const int tok0 = cu_q[r], q_len = cu_q[r + 1] - tok0;
@@ -238,7 +238,8 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
   for (int i = 0; i < 2; ++i) {
     const int row = m0 + warp * 16 + g + 8 * i;
     if (row >= q_len) continue;
-    const float inv = 1.0f / l_run[i];
+    // a sink: one more term of score 0 in the denominator, with no value
+    const float inv = 1.0f / (l_run[i] + (sink ? exp2f(-m_run[i]) : 0.f));
     __nv_bfloat16* dst = out + ((size_t)(tok0 + row) * nq + head) * D + 2 * t;
 #pragma unroll
     for (int dt = 0; dt < DTILES; ++dt)
@@ -269,7 +270,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
                    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                    const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ kv_len_ptr,
                    const int* __restrict__ page_indptr, const int* __restrict__ page_indices, int nq, int nkv,
-                   float scale_log2, int window, int page_shift, int num_splits, int* __restrict__ counters,
+                   float scale_log2, int window, int sink, int page_shift, int num_splits, int* __restrict__ counters,
                    int cluster_merge) {
   // Until pdl_wait() below, only data written before this step is touched: the step's metadata and
   // the keys and values of older tokens. So the CTA may start streaming them while the kernels
@@ -478,6 +479,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
           l += wgt * ls[i];
         }
       }
+      if (sink) l += exp2f(-m);
       out[((size_t)r * nq + head0 + row) * D + c] = __float2bfloat16_rn(acc / l);
     }
     cluster.sync();  // shared memory lives until every CTA of the cluster has read it
@@ -499,6 +501,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
     }
     const int head = head0 + row;
     if (num_splits == 1) {
+      if (sink) l += exp2f(-m);
       out[((size_t)r * nq + head) * D + c] = __float2bfloat16_rn(acc / l);
     } else {
       const size_t p = ((size_t)r * nq + head) * num_splits + split;
@@ -556,13 +559,14 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
         l += wgt * mls[i].y;
       }
     }
+    if (sink) l += exp2f(-m);
     out[item * D + c] = __float2bfloat16_rn(acc / l);
   }
 }
 
 // out[r, head] = sum_s w_s O_s / sum_s w_s l_s with w_s = 2^(m_s - max m)
 __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
-                                         const float* __restrict__ part_ml, int num_splits) {
+                                         const float* __restrict__ part_ml, int num_splits, int sink) {
   pdl_prologue();
   const size_t item = blockIdx.x;  // r * nq + head
   const float* ml = part_ml + item * num_splits * 2;
@@ -576,6 +580,7 @@ __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, const 
       acc += wgt * part_o[(item * num_splits + s) * D + c];
       l += wgt * ml[2 * s + 1];
     }
+    if (sink) l += exp2f(-m);
     out[item * D + c] = __float2bfloat16_rn(acc / l);
   }
 }
@@ -601,7 +606,7 @@ static int shift_of(int page_size) {
 
 MS_EXPORT int MS_ATTN_FN(prefill)(void* out, const void* q, const void* k_pool, const void* v_pool, const int* cu_q,
                                   const int* q_start, const int* page_indptr, const int* page_indices, int num_rows,
-                                  int max_q_len, int nq, int nkv, float scale, int window, int page_size,
+                                  int max_q_len, int nq, int nkv, float scale, int window, int sink, int page_size,
                                   cudaStream_t stream) {
   if (num_rows == 0) return 0;
   MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
@@ -619,7 +624,7 @@ MS_EXPORT int MS_ATTN_FN(prefill)(void* out, const void* q, const void* k_pool, 
   dim3 grid(ceil_div(max_q_len, PF_BM), num_rows, nq);
   MS_LAUNCH(attn_prefill_kernel, grid, PF_THREADS, smem, stream,
       (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, cu_q,
-      q_start, page_indptr, page_indices, nq, nkv, scale * LOG2E, window, shift_of(page_size));
+      q_start, page_indptr, page_indices, nq, nkv, scale * LOG2E, window, sink, shift_of(page_size));
   MS_CHECK_LAUNCH();
   return 0;
 }
@@ -627,7 +632,7 @@ MS_EXPORT int MS_ATTN_FN(prefill)(void* out, const void* q, const void* k_pool, 
 MS_EXPORT int MS_ATTN_FN(decode_fused)(void* out, void* part_o, void* part_ml, int* counters, const void* q,
                                        const void* k_pool, const void* v_pool, const int* kv_len,
                                        const int* page_indptr, const int* page_indices, int num_rows, int nq, int nkv,
-                                       float scale, int window, int page_size, int num_splits, cudaStream_t stream);
+                                       float scale, int window, int sink, int page_size, int num_splits, cudaStream_t stream);
 
 // The decode kernel's shared-memory attribute belongs to a device: set once for each.
 static int configure_decode() {
@@ -645,10 +650,10 @@ static int configure_decode() {
 // Scratch for num_splits > 1: part_o [rows, nq, splits, D] floats and part_ml [rows, nq, splits, 2] floats.
 MS_EXPORT int MS_ATTN_FN(decode)(void* out, void* part_o, void* part_ml, const void* q, const void* k_pool,
                                  const void* v_pool, const int* kv_len, const int* page_indptr,
-                                 const int* page_indices, int num_rows, int nq, int nkv, float scale, int window,
+                                 const int* page_indices, int num_rows, int nq, int nkv, float scale, int window, int sink,
                                  int page_size, int num_splits, cudaStream_t stream) {
   return MS_ATTN_FN(decode_fused)(out, part_o, part_ml, nullptr, q, k_pool, v_pool, kv_len, page_indptr, page_indices,
-                                  num_rows, nq, nkv, scale, window, page_size, num_splits, stream);
+                                  num_rows, nq, nkv, scale, window, sink, page_size, num_splits, stream);
 }
 
 // As above; with `counters` (num_rows * kv_heads * ceil(group / 16) ints, zero before the first
@@ -657,7 +662,7 @@ MS_EXPORT int MS_ATTN_FN(decode)(void* out, void* part_o, void* part_ml, const v
 MS_EXPORT int MS_ATTN_FN(decode_fused)(void* out, void* part_o, void* part_ml, int* counters, const void* q,
                                        const void* k_pool, const void* v_pool, const int* kv_len,
                                        const int* page_indptr, const int* page_indices, int num_rows, int nq, int nkv,
-                                       float scale, int window, int page_size, int num_splits, cudaStream_t stream) {
+                                       float scale, int window, int sink, int page_size, int num_splits, cudaStream_t stream) {
   if (num_rows == 0) return 0;
   MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
   MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "attention: page_size=%d must be a power of two", page_size);
@@ -669,11 +674,11 @@ MS_EXPORT int MS_ATTN_FN(decode_fused)(void* out, void* part_o, void* part_ml, i
   dim3 grid(num_splits, num_rows, nkv * ceil_div(group, 16));
   MS_LAUNCH(attn_decode_kernel, grid, DC_THREADS, DecodeSmem::bytes, stream,
       (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
-      (const __nv_bfloat16*)v_pool, kv_len, page_indptr, page_indices, nq, nkv, scale * LOG2E, window,
+      (const __nv_bfloat16*)v_pool, kv_len, page_indptr, page_indices, nq, nkv, scale * LOG2E, window, sink,
       shift_of(page_size), num_splits, counters, 0);
   if (num_splits > 1 && counters == nullptr) {
     MS_LAUNCH(attn_decode_merge_kernel, num_rows * nq, D >= 128 ? 128 : 64, 0, stream, (__nv_bfloat16*)out,
-              (const float*)part_o, (const float*)part_ml, num_splits);
+              (const float*)part_o, (const float*)part_ml, num_splits, sink);
   }
   return 0;
 }
@@ -683,7 +688,7 @@ MS_EXPORT int MS_ATTN_FN(decode_fused)(void* out, void* part_o, void* part_ml, i
 // distributed shared memory, so no scratch, no fence and no ticket are needed.
 MS_EXPORT int MS_ATTN_FN(decode_cluster)(void* out, const void* q, const void* k_pool, const void* v_pool, const int* kv_len,
                                          const int* page_indptr, const int* page_indices, int num_rows, int nq, int nkv,
-                                         float scale, int window, int page_size, int num_splits, cudaStream_t stream) {
+                                         float scale, int window, int sink, int page_size, int num_splits, cudaStream_t stream) {
   if (num_rows == 0) return 0;
   MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
   MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "attention: page_size=%d must be a power of two", page_size);
@@ -694,7 +699,7 @@ MS_EXPORT int MS_ATTN_FN(decode_cluster)(void* out, const void* q, const void* k
   dim3 grid(num_splits, num_rows, nkv * ceil_div(group, 16));
   MS_LAUNCH_CLUSTERED(attn_decode_kernel, grid, DC_THREADS, DecodeSmem::bytes, stream, num_splits,
       (__nv_bfloat16*)out, (float*)nullptr, (float*)nullptr, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
-      (const __nv_bfloat16*)v_pool, kv_len, page_indptr, page_indices, nq, nkv, scale * LOG2E, window,
+      (const __nv_bfloat16*)v_pool, kv_len, page_indptr, page_indices, nq, nkv, scale * LOG2E, window, sink,
       shift_of(page_size), num_splits, (int*)nullptr, 1);
   return 0;
 }
@@ -777,5 +782,5 @@ MS_EXPORT int MS_ATTN_FN(decode_noalloc)(void* out, const void* q, const void* k
     part_ml = base + items * D;  // [rows, heads, splits, 2]
   }
   return MS_ATTN_FN(decode)(out, part_o, part_ml, q, k_pool, v_pool, kv_len, page_indptr, page_indices, num_rows, nq, nkv,
-                            scale, window, page_size, num_splits, stream);
+                            scale, window, 0, page_size, num_splits, stream);
 }

@@ -28,7 +28,7 @@ attention_rowwise_kernel(T* __restrict__ out,            // [T, nq, d]
                          const T* __restrict__ v_pool,
                          const int* __restrict__ positions, const int* __restrict__ row_of_token,
                          const int* __restrict__ page_indptr, const int* __restrict__ page_indices,
-                         int num_tokens, int nq, int nkv, int d, float scale, int window, int page_shift,
+                         int num_tokens, int nq, int nkv, int d, float scale, int window, int sink, int page_shift,
                          int num_pages, int* __restrict__ status) {
   extern __shared__ float q_smem[];  // [warps][d]
   pdl_prologue();
@@ -94,6 +94,7 @@ attention_rowwise_kernel(T* __restrict__ out,            // [T, nq, d]
     }
     m = m_new;
   }
+  if (sink) l += expf(-m);  // one more term of score 0 in the denominator, with no value
   T* o = out + ((size_t)t * nq + h) * d;
 #pragma unroll
   for (int i = 0; i < ROWWISE_MAX_D / 32; ++i) {
@@ -109,7 +110,7 @@ using namespace ms;
 MS_EXPORT int ms_attention_rowwise(void* out, const void* q, const void* k_pool, const void* v_pool,
                                    const int* positions, const int* row_of_token, const int* page_indptr,
                                    const int* page_indices, int num_tokens, int nq, int nkv, int head_dim, float scale,
-                                   int window, int page_size, int num_pages, int* status, int dtype, cudaStream_t stream) {
+                                   int window, int sink, int page_size, int num_pages, int* status, int dtype, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
   MS_CHECK_ARG(head_dim > 0 && head_dim <= ROWWISE_MAX_D, "attention: head_dim=%d is outside 1..%d", head_dim, ROWWISE_MAX_D);
@@ -123,11 +124,11 @@ MS_EXPORT int ms_attention_rowwise(void* out, const void* q, const void* k_pool,
   if (dtype == MS_F32)
     MS_LAUNCH(attention_rowwise_kernel<float>, blocks, warps * 32, smem, stream,
         (float*)out, (const float*)q, (const float*)k_pool, (const float*)v_pool, positions, row_of_token, page_indptr,
-        page_indices, num_tokens, nq, nkv, head_dim, scale, window, page_shift, num_pages, status);
+        page_indices, num_tokens, nq, nkv, head_dim, scale, window, sink, page_shift, num_pages, status);
   else
     MS_LAUNCH(attention_rowwise_kernel<__nv_bfloat16>, blocks, warps * 32, smem, stream,
         (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
-        positions, row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, head_dim, scale, window, page_shift,
+        positions, row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, head_dim, scale, window, sink, page_shift,
         num_pages, status);
   return 0;
 }

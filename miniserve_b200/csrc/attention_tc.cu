@@ -359,7 +359,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ cu_q, const int* __restrict__ q_start, const int* __restrict__ page_indptr,
-                        const int* __restrict__ page_indices, int nq, int nkv, float scale_log2, int page_shift,
+                        const int* __restrict__ page_indices, int nq, int nkv, float scale_log2, int sink, int page_shift,
                         const AtGrid gr_given, int* __restrict__ status,
                         float* __restrict__ part_o, float2* __restrict__ part_ml, int* __restrict__ queue,
                         int* __restrict__ tickets, const int* __restrict__ plan) {
@@ -643,7 +643,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         __nv_bfloat16* dst = out + item * AT_D;
         if (it.shares[g] <= 1) {
           if (ok && n_mine > 0) {
-            const float inv = 1.0f / l_sum;
+            // a sink: one more term of score 0 in the denominator, with no value
+            const float inv = 1.0f / (l_sum + (sink ? at_ex2(-m_used * scale_log2) : 0.f));
   #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
               float ov[32];
@@ -715,6 +716,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               const float2 ml = sp == split ? make_float2(m_used, l_sum) : __ldcg(&pml[sp * 128]);
               l_all += ml.y == 0.f ? 0.f : at_ex2((ml.x - m_all) * scale_log2) * ml.y;
             }
+            if (sink) l_all += at_ex2(-m_all * scale_log2);
             const float inv = 1.0f / l_all;
   #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
@@ -858,7 +860,7 @@ MS_EXPORT void ms_attn_tc_scratch(int max_q_len, int num_rows, int nq, int nkv, 
 MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, const void* v_pool, const int* cu_q,
                                  const int* q_start, const int* page_indptr, const int* page_indices, int num_rows,
                                  int num_tokens, int max_q_len, int nq, int nkv, long long pool_pages, float scale,
-                                 int window, int page_size, int* status, int splits, int min_tiles, float* partials,
+                                 int window, int sink, int page_size, int* status, int splits, int min_tiles, float* partials,
                                  int* queue, const int* plan, cudaStream_t stream) {
   // plan: null, or four device ints (tiles of queries per row, rows, key splits, least key tiles per split) that
   // ms_attn_tc_write_plan fills before the launch runs; num_rows, max_q_len, splits and min_tiles are then unused
@@ -924,7 +926,7 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
   // one CTA fills an SM (192 KB of shared memory, all of tensor memory) and takes items until none is left
   const unsigned grid = (unsigned)(plan == nullptr && total < sm_count ? total : sm_count);
   MS_LAUNCH(attn_prefill_tc_kernel, grid, AT_THREADS, smem_bytes, stream, map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q,
-            q_start, page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, page_shift, gr, status,
+            q_start, page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, sink, page_shift, gr, status,
             partials, reinterpret_cast<float2*>(partials + (total / gr.splits) * 2 * gr.splits * (AT_ROWS * AT_D)), queue,
             queue + 2, plan);
   return 0;

@@ -1,0 +1,249 @@
+// Pointwise kernels around mixers and feed-forwards that are not Qwen3's:
+//
+//   * Dynamic Tanh in the place of a norm, y = tanh(alpha x) w + b, with the residual add (and an
+//     optional row gather) fused in as in add_rmsnorm: no statistic is taken, so a row needs no reduction;
+//   * the tanh form of GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)));
+//   * the step between a q|k|v(|gate) projection and attention for heads whose key size and value size
+//     differ and whose rotation pairs either adjacent channels (2i, 2i+1) or the two halves (i, i+rot/2):
+//     per-head RMS norm of q and k, rotation of the first `rot` channels, q written out and k, v written
+//     into their pages, each padded with zeros to the cache's head size D >= max(dk, dv). A zero channel
+//     adds nothing to a score and yields a zero output channel, so attention over the padded heads is
+//     attention over the real ones;
+//   * a sigmoid gate per (token, head) on attention's output, with a scale, written at a column offset
+//     of a wider row (the input of an output projection shared with another branch);
+//   * a x + b y, and an in-place scale of float32 logits.
+//
+// Norm statistics, angles, gates and the tanh are float32; each output is rounded once.
+#include "common.cuh"
+
+namespace ms {
+
+template <typename T>
+__global__ void add_dyt_kernel(T* __restrict__ out, float* __restrict__ residual, const T* __restrict__ delta,
+                               const float* __restrict__ w, const float* __restrict__ b, const float* __restrict__ alpha,
+                               const int* __restrict__ rows, int hidden, int write_residual) {
+  pdl_prologue();
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* res = residual + (size_t)r * hidden;
+  const T* dl = delta ? delta + (size_t)r * hidden : nullptr;
+  const float a = alpha[0];
+  T* o = out + (size_t)i * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float h = res[c];
+    if (dl) {
+      h += Elem<T>::load(dl + c);
+      if (write_residual) res[c] = h;
+    }
+    Elem<T>::store(o + c, tanhf(a * h) * w[c] + b[c]);
+  }
+}
+
+template <typename T>
+__global__ void gelu_tanh_kernel(T* __restrict__ out, const T* __restrict__ x, long long n) {
+  pdl_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float z = Elem<T>::load(x + i);
+  Elem<T>::store(out + i, 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))));
+}
+
+__global__ void scale_f32_kernel(float* __restrict__ x, float s, long long n) {
+  pdl_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] *= s;
+}
+
+template <typename T>
+__global__ void axpby_kernel(T* __restrict__ out, const T* __restrict__ x, const T* __restrict__ y, float a, float b, long long n) {
+  pdl_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) Elem<T>::store(out + i, a * Elem<T>::load(x + i) + b * Elem<T>::load(y + i));
+}
+
+// out[t, h * dv + c] = scale * sigmoid(gate[t, h]) * attn[t, h, c]   (c < dv; attn rows are D wide)
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ out, int ld_out, const T* __restrict__ attn, const T* __restrict__ gate,
+                                 int ld_gate, long long items, int nq, int d_pad, int dv, float scale, int gated) {
+  pdl_prologue();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= items) return;
+  const int c = (int)(idx % dv);
+  const long long th = idx / dv;
+  const int h = (int)(th % nq);
+  const long long t = th / nq;
+  float g = scale;
+  if (gated) g *= 1.0f / (1.0f + expf(-Elem<T>::load(gate + t * ld_gate + h)));
+  Elem<T>::store(out + t * ld_out + (size_t)h * dv + c, g * Elem<T>::load(attn + (t * nq + h) * d_pad + c));
+}
+
+// One warp per (token, head) over the nq query heads, nkv key heads and nkv value heads of a token.
+template <typename T>
+__global__ void qkv_prepare_kernel(
+    T* __restrict__ q_out,             // [T, nq, D]
+    T* __restrict__ k_pool,            // [pages, nkv, page_size, D]
+    T* __restrict__ v_pool,
+    const T* __restrict__ proj, int ld, int q_off, int k_off, int v_off,   // columns of the projection's rows
+    const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w,  // [dk] or null
+    const float* __restrict__ cos_sin,  // [T, rot]: cos then sin of every (token, pair); null when rot == 0
+    const int* __restrict__ positions, const int* __restrict__ row_of_token, const int* __restrict__ page_indptr,
+    const int* __restrict__ page_indices, int num_tokens, int nq, int nkv, int dk, int dv, int d_pad, int rot,
+    int adjacent, float eps, int page_shift, int num_pages, int* __restrict__ status) {
+  pdl_prologue();
+  const int lane = threadIdx.x & 31;
+  const int heads_total = nq + 2 * nkv;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long long)num_tokens * heads_total) return;
+  const int t = (int)(item / heads_total);
+  const int h = (int)(item - (long long)t * heads_total);
+  const T* row_in = proj + (size_t)t * ld;
+  const int pos = positions[t];
+  const T* src;
+  T* dst;
+  const float* nw = nullptr;
+  bool is_v = false;
+  if (h < nq) {
+    src = row_in + q_off + (size_t)h * dk;
+    dst = q_out + ((size_t)t * nq + h) * d_pad;
+    nw = q_norm_w;
+  } else {
+    const int kvh = (h - nq) % nkv;
+    is_v = (h - nq) >= nkv;
+    const int row = row_of_token[t];
+    const int page_size = 1 << page_shift;
+    const int page = page_indices[page_indptr[row] + (pos >> page_shift)];
+    if (page < 0) {
+      if (lane == 0) atomicExch(status, 2);
+      return;
+    }
+    MS_DEBUG_ONLY(if (page >= num_pages || row < 0) {
+      if (lane == 0) atomicExch(status, 5);
+      return;
+    })
+    dst = (is_v ? v_pool : k_pool) + (((size_t)page * nkv + kvh) * page_size + (pos & (page_size - 1))) * d_pad;
+    src = is_v ? row_in + v_off + (size_t)kvh * dv : row_in + k_off + (size_t)kvh * dk;
+    nw = k_norm_w;
+  }
+  if (is_v) {
+    for (int c = lane; c < d_pad; c += 32) Elem<T>::store(dst + c, c < dv ? Elem<T>::load(src + c) : 0.f);
+    return;
+  }
+  float inv = 1.f;
+  if (nw) {
+    float ss = 0.f;
+    for (int c = lane; c < dk; c += 32) {
+      const float x = Elem<T>::load(src + c);
+      ss += x * x;
+    }
+    ss = warp_sum(ss);
+    inv = 1.0f / sqrtf(ss / (float)dk + eps);
+  }
+  const int half = rot >> 1;
+  for (int j = lane; j < half; j += 32) {
+    const int ia = adjacent ? 2 * j : j, ib = adjacent ? 2 * j + 1 : j + half;
+    float a = Elem<T>::load(src + ia), b = Elem<T>::load(src + ib);
+    if (nw) {
+      a = (a * inv) * nw[ia];
+      b = (b * inv) * nw[ib];
+    }
+    const float cs = cos_sin[(size_t)t * rot + j], sn = cos_sin[(size_t)t * rot + half + j];
+    Elem<T>::store(dst + ia, a * cs - b * sn);
+    Elem<T>::store(dst + ib, b * cs + a * sn);
+  }
+  for (int c = rot + lane; c < d_pad; c += 32) {
+    float x = 0.f;
+    if (c < dk) {
+      x = Elem<T>::load(src + c);
+      if (nw) x = (x * inv) * nw[c];
+    }
+    Elem<T>::store(dst + c, x);
+  }
+}
+
+}  // namespace ms
+
+using namespace ms;
+
+MS_EXPORT int ms_add_dyt(void* out, float* residual, const void* delta, const float* w, const float* b, const float* alpha,
+                         const int* rows, int n, int hidden, int write_residual, int dtype, cudaStream_t stream) {
+  if (n == 0) return 0;
+  MS_CHECK_ARG(hidden > 0, "add_dyt: hidden=%d", hidden);
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (dtype == MS_F32)
+    MS_LAUNCH(add_dyt_kernel<float>, n, threads, 0, stream, (float*)out, residual, (const float*)delta, w, b, alpha, rows, hidden,
+              write_residual);
+  else
+    MS_LAUNCH(add_dyt_kernel<__nv_bfloat16>, n, threads, 0, stream, (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta, w, b,
+              alpha, rows, hidden, write_residual);
+  return 0;
+}
+
+MS_EXPORT int ms_gelu_tanh(void* out, const void* x, long long n, int dtype, cudaStream_t stream) {
+  if (n == 0) return 0;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (dtype == MS_F32)
+    MS_LAUNCH(gelu_tanh_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)x, n);
+  else
+    MS_LAUNCH(gelu_tanh_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, n);
+  return 0;
+}
+
+MS_EXPORT int ms_scale_f32(float* x, float s, long long n, cudaStream_t stream) {
+  if (n == 0) return 0;
+  MS_LAUNCH(scale_f32_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, x, s, n);
+  return 0;
+}
+
+MS_EXPORT int ms_axpby(void* out, const void* x, const void* y, float a, float b, long long n, int dtype, cudaStream_t stream) {
+  if (n == 0) return 0;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (dtype == MS_F32)
+    MS_LAUNCH(axpby_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)x, (const float*)y, a, b, n);
+  else
+    MS_LAUNCH(axpby_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)x,
+              (const __nv_bfloat16*)y, a, b, n);
+  return 0;
+}
+
+MS_EXPORT int ms_head_gate(void* out, int ld_out, const void* attn, const void* gate, int ld_gate, int num_tokens, int nq,
+                           int d_pad, int dv, float scale, int dtype, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  MS_CHECK_ARG(nq > 0 && dv > 0 && dv <= d_pad, "head_gate: bad sizes nq=%d dv=%d D=%d", nq, dv, d_pad);
+  const long long items = (long long)num_tokens * nq * dv;
+  const unsigned blocks = (unsigned)((items + 255) / 256);
+  if (dtype == MS_F32)
+    MS_LAUNCH(head_gate_kernel<float>, blocks, 256, 0, stream, (float*)out, ld_out, (const float*)attn, (const float*)gate, ld_gate,
+              items, nq, d_pad, dv, scale, gate != nullptr);
+  else
+    MS_LAUNCH(head_gate_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, ld_out, (const __nv_bfloat16*)attn,
+              (const __nv_bfloat16*)gate, ld_gate, items, nq, d_pad, dv, scale, gate != nullptr);
+  return 0;
+}
+
+MS_EXPORT int ms_qkv_prepare(void* q_out, void* k_pool, void* v_pool, const void* proj, int ld, int q_off, int k_off, int v_off,
+                             const float* q_norm_w, const float* k_norm_w, const float* cos_sin, const int* positions,
+                             const int* row_of_token, const int* page_indptr, const int* page_indices, int num_tokens, int nq,
+                             int nkv, int dk, int dv, int d_pad, int rot, int adjacent, float eps, int page_size, int num_pages,
+                             int* status, int dtype, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  MS_CHECK_ARG(nq > 0 && nkv > 0 && dk > 0 && dv > 0 && d_pad >= dk && d_pad >= dv, "qkv_prepare: bad sizes nq=%d nkv=%d dk=%d dv=%d D=%d",
+               nq, nkv, dk, dv, d_pad);
+  MS_CHECK_ARG(rot >= 0 && rot <= dk && rot % 2 == 0, "qkv_prepare: rot=%d must be even and at most dk=%d", rot, dk);
+  MS_CHECK_ARG(rot == 0 || cos_sin != nullptr, "qkv_prepare: a rotation needs the step's cos/sin table");
+  MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "qkv_prepare: page_size=%d must be a power of two", page_size);
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  const long long items = (long long)num_tokens * (nq + 2 * nkv);
+  const int warps = 8;
+  const unsigned blocks = (unsigned)((items + warps - 1) / warps);
+  if (dtype == MS_F32)
+    MS_LAUNCH(qkv_prepare_kernel<float>, blocks, warps * 32, 0, stream, (float*)q_out, (float*)k_pool, (float*)v_pool,
+              (const float*)proj, ld, q_off, k_off, v_off, q_norm_w, k_norm_w, cos_sin, positions, row_of_token, page_indptr,
+              page_indices, num_tokens, nq, nkv, dk, dv, d_pad, rot, adjacent, eps, page_shift, num_pages, status);
+  else
+    MS_LAUNCH(qkv_prepare_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
+              (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)proj, ld, q_off, k_off, v_off, q_norm_w, k_norm_w, cos_sin, positions,
+              row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, dk, dv, d_pad, rot, adjacent, eps, page_shift,
+              num_pages, status);
+  return 0;
+}

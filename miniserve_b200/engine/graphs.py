@@ -178,11 +178,8 @@ class DecodeGraphs:
         # capturing). It runs the step's real rows, so what it changes has to be put back: rewriting the same
         # keys and values is harmless, but a mixer's per-request state would otherwise advance twice (by the
         # warm-up and again by the first replay).
-        from ..cache.manager import StateEntryView
-
         slots = ctx.state_slot.long()
-        states = {id(v.state): v.state for v in sf.cache.entry_views if isinstance(v, StateEntryView) and v.state is not None}
-        kept = [(st, st[slots].clone()) for st in states.values()]
+        kept = [(st, st[slots].clone()) for st in sf.cache.state_tensors()]
         with torch.cuda.stream(s):
             s.wait_stream(torch.cuda.current_stream(sf.device))
             self._forward(ctx, bucket, mode, klass, f32, i64)

@@ -36,7 +36,7 @@ def load_model(model_dir: str | Path, dtype: str | torch.dtype = "bfloat16",
     """(raw config.json, typed configuration, model) for a folder with config.json and
     safetensors; the model class is chosen by ``architectures`` in config.json."""
     raw = load_config_dict(model_dir)
-    _, cfg, spec = resolve(raw)
+    _, cfg, spec = resolve(raw, model_dir)
     model = DecoderModel(spec, parse_dtype(dtype), device)
     tensors = load_weights(model_dir, model.weight_decls(), model.dtype, model.device, ignorable=_ignorable(model),
                            rules=spec.checkpoint_rules, stacks=model.weight_stacks())

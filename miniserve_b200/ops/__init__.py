@@ -12,6 +12,8 @@ import ctypes
 import torch
 
 from . import blas, native
+from .mixers import (add_dyt, axpby, conv_silu_unit, conv_state_update, decay_scan, gelu_tanh, head_gate,  # noqa: F401
+                     head_norm_gate, qkv_prepare, scale_)
 from .native import NativeError, OutOfBlocks
 
 __all__ = [
@@ -414,7 +416,7 @@ def rope_table_tiled(table: torch.Tensor, stream=None) -> torch.Tensor:
 def attention_rowwise(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                       positions: torch.Tensor, row_of_token: torch.Tensor, page_indptr: torch.Tensor,
                       page_indices: torch.Tensor, scale: float, window: int | None, status: torch.Tensor,
-                      stream=None) -> None:
+                      stream=None, sink: bool = False) -> None:
     """Causal attention of every new token over its request's pages; one warp per (token, head),
     float32 arithmetic in a fixed order (bit-identical however the tokens were batched)."""
     _check_dev(out, q, k_pool, v_pool, positions, row_of_token, page_indptr, page_indices, status)
@@ -424,7 +426,7 @@ def attention_rowwise(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, 
     k = native.kernels()
     native.kernel_check(k.ms_attention_rowwise(
         _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(positions), _ptr(row_of_token), _ptr(page_indptr),
-        _ptr(page_indices), t, nq, nkv, d, float(scale), int(window or 0), page_size, k_pool.shape[0], _ptr(status),
+        _ptr(page_indices), t, nq, nkv, d, float(scale), int(window or 0), int(sink), page_size, k_pool.shape[0], _ptr(status),
         dtype_code(q.dtype), _stream(stream)))
 
 
@@ -456,8 +458,9 @@ def sample(tokens: torch.Tensor, logits: torch.Tensor, temperature: torch.Tensor
 
 
 def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
-              scale: float, window: int | None) -> None:
+              scale: float, window: int | None, sink: bool = False) -> None:
     """Causal attention of the step's new tokens over the paged cache of cache group ``group``.
+    ``sink``: one more term of score 0 in the softmax's denominator, which carries no value.
 
     float32 runs the row-wise kernel (bit-identical however the step was cut). bfloat16 runs the
     tensor-core kernels when they take this head size, else the row-wise kernel too."""
@@ -478,15 +481,15 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
                 inside = ctx.graph_bucket
                 ctx.graph_bucket = ctx.graph_bucket or single
                 try:
-                    attention_bf16.run_decode(out, q, k_pool, v_pool, ctx, group, scale, window, single)
+                    attention_bf16.run_decode(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink)
                 finally:
                     ctx.graph_bucket = inside
             if single < ctx.num_rows:
-                _attention_tc_planned(out, q, k_pool, v_pool, ctx, group, scale, window, recorder, single)
+                _attention_tc_planned(out, q, k_pool, v_pool, ctx, group, scale, window, recorder, single, sink)
             return
         # Else the call is left out of the graphs and made again for every step that replays them, with
         # that step's context (the operand tensors are the captured pass's own and do not move).
-        recorder.defer(lambda step: attention(out, q, k_pool, v_pool, step, group, scale, window))
+        recorder.defer(lambda step: attention(out, q, k_pool, v_pool, step, group, scale, window, sink))
         return
     if q.dtype == torch.bfloat16:
         # rows at the front that bring one token each (a decode step, or the decoding requests
@@ -494,17 +497,17 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
         split_ok = attention_bf16.supports(q.shape[2], k_pool.shape[2])
         single = ctx.leading_single_rows if split_ok else 0
         if single:
-            attention_bf16.run_decode(out, q, k_pool, v_pool, ctx, group, scale, window, single)
+            attention_bf16.run_decode(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink)
         if single == ctx.num_rows:
             return
         if attention_tc_ok(q, k_pool):
-            attention_tc_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single)
+            attention_tc_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink)
             return
         if split_ok:
-            attention_bf16.run_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single)
+            attention_bf16.run_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink)
             return
     attention_rowwise(out, q, k_pool, v_pool, ctx.positions, ctx.row_of_token, ctx.page_indptr[group],
-                      ctx.page_indices[group], scale, window, ctx.status, stream=ctx.stream)
+                      ctx.page_indices[group], scale, window, ctx.status, stream=ctx.stream, sink=sink)
 
 
 _ATTN_TC_SCRATCH_LIMIT = 1 << 29  # bytes of partial results that a step's attention may ask for
@@ -522,7 +525,7 @@ _ATTN_TC_PLANNED_SCRATCH = 1 << 25  # floats of partial results that a captured 
 
 
 def _attention_tc_planned(out, q, k_pool, v_pool, ctx, group: int, scale: float, window: int | None, recorder,
-                          first_row: int = 0) -> None:
+                          first_row: int = 0, sink: bool = False) -> None:
     """The tcgen05 attention of the rows from ``first_row`` on, launched so that a CUDA graph can hold it:
     one CTA per SM, the plan of those rows (query tiles, rows, key splits) read from device memory.
     Launches with the same heads and window in one pass share the plan, which ``recorder`` has
@@ -558,13 +561,13 @@ def _attention_tc_planned(out, q, k_pool, v_pool, ctx, group: int, scale: float,
     skip = 4 * first_row  # the per-row tables are int32
     native.kernel_check(lib.ms_attn_tc_prefill(
         _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(ctx.cu_q) + skip, _ptr(ctx.q_start) + skip, _ptr(ctx.page_indptr[group]) + skip,
-        _ptr(ctx.page_indices[group]), 0, t, 0, nq, nkv, k_pool.shape[0], float(scale), int(window or 0), k_pool.shape[2],
+        _ptr(ctx.page_indices[group]), 0, t, 0, nq, nkv, k_pool.shape[0], float(scale), int(window or 0), int(sink), k_pool.shape[2],
         _ptr(device_status(q.device)), 0, 0, _ptr(part), _ptr(queue), _ptr(plan), ctx.stream),
         lib=lib, errfn="ms_attn_tc_last_error")
 
 
 def attention_tc_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
-                         scale: float, window: int | None, first_row: int = 0) -> None:
+                         scale: float, window: int | None, first_row: int = 0, sink: bool = False) -> None:
     """Causal attention of rows [first_row, num_rows) of the step, any number of new tokens each,
     on the tcgen05 tensor cores (``csrc/attention_tc.cu``)."""
     _check_dev(out, q, k_pool, v_pool)
@@ -607,5 +610,5 @@ def attention_tc_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tenso
     native.kernel_check(lib.ms_attn_tc_prefill(
         _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(ctx.cu_q) + skip, _ptr(ctx.q_start) + skip, _ptr(ctx.page_indptr[group]) + skip,
         _ptr(ctx.page_indices[group]), rows, t, ctx.max_q_len, nq, k_pool.shape[1], k_pool.shape[0], float(scale),
-        int(window or 0), k_pool.shape[2], _ptr(device_status(q.device)), splits, min_tiles, _ptr(part), _ptr(queue), None, ctx.stream),
+        int(window or 0), int(sink), k_pool.shape[2], _ptr(device_status(q.device)), splits, min_tiles, _ptr(part), _ptr(queue), None, ctx.stream),
         lib=lib, errfn="ms_attn_tc_last_error")

@@ -40,10 +40,10 @@ def _lib(head_dim: int):
     fns = {}
     for name, args, res in (
         ("last_error", [], c_char_p),
-        ("prefill", [_p] * 8 + [_i, _i, _i, _i, _f, _i, _i, _p], c_int),
-        ("decode", [_p] * 9 + [_i, _i, _i, _f, _i, _i, _i, _p], c_int),
-        ("decode_fused", [_p] * 10 + [_i, _i, _i, _f, _i, _i, _i, _p], c_int),
-        ("decode_cluster", [_p] * 7 + [_i, _i, _i, _f, _i, _i, _i, _p], c_int),
+        ("prefill", [_p] * 8 + [_i, _i, _i, _i, _f, _i, _i, _i, _p], c_int),
+        ("decode", [_p] * 9 + [_i, _i, _i, _f, _i, _i, _i, _i, _p], c_int),
+        ("decode_fused", [_p] * 10 + [_i, _i, _i, _f, _i, _i, _i, _i, _p], c_int),
+        ("decode_cluster", [_p] * 7 + [_i, _i, _i, _f, _i, _i, _i, _i, _p], c_int),
         ("decode_clusters_resident", [_i, ctypes.POINTER(c_int)], c_int),
     ):
         fn = getattr(lib, pre + name)
@@ -120,18 +120,18 @@ def _scratch(ctx, rows: int, nq: int, splits: int, d: int, device) -> tuple[torc
 
 
 def run(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
-        scale: float, window: int | None) -> None:
+        scale: float, window: int | None, sink: bool = False) -> None:
     """The step's attention: rows at the front that bring one token each go to the split-key
     decode kernel, the rest to the tiled kernel."""
     single = ctx.leading_single_rows
     if single:
-        run_decode(out, q, k_pool, v_pool, ctx, group, scale, window, single)
+        run_decode(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink)
     if single < ctx.num_rows:
-        run_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single)
+        run_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink)
 
 
 def run_decode(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
-               scale: float, window: int | None, rows: int) -> None:
+               scale: float, window: int | None, rows: int, sink: bool = False) -> None:
     """Rows [0, rows) of the step, one new token each (so token i belongs to row i): keys split
     across CTAs, partial results merged by the last CTA of each (row, head group) to finish."""
     t, nq, d = q.shape
@@ -146,7 +146,7 @@ def run_decode(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool:
         # the splits as one thread-block cluster: merged through distributed shared memory
         _check(fns, fns["decode_cluster"](
             out.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.kv_len.data_ptr(), indptr.data_ptr(),
-            indices.data_ptr(), rows, nq, nkv, float(scale), int(window or 0), page_size, splits, ctx.stream))
+            indices.data_ptr(), rows, nq, nkv, float(scale), int(window or 0), int(sink), page_size, splits, ctx.stream))
         return
     part_o = part_ml = counters = None
     if splits > 1:
@@ -161,12 +161,12 @@ def run_decode(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool:
     _check(fns, fns["decode_fused"](
         out.data_ptr(), None if part_o is None else part_o.data_ptr(), None if part_ml is None else part_ml.data_ptr(),
         None if counters is None else counters.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.kv_len.data_ptr(), indptr.data_ptr(),
-        indices.data_ptr(), rows, nq, nkv, float(scale), int(window or 0), page_size, splits, ctx.stream),
+        indices.data_ptr(), rows, nq, nkv, float(scale), int(window or 0), int(sink), page_size, splits, ctx.stream),
         launches=1)
 
 
 def run_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
-                scale: float, window: int | None, first_row: int = 0) -> None:
+                scale: float, window: int | None, first_row: int = 0, sink: bool = False) -> None:
     """Rows [first_row, num_rows) of the step, any number of new tokens each: tiles of 64 queries
     over the row's pages (``mma.sync``; the tcgen05 kernel of ``attention_tc.cu`` takes head size 128)."""
     t, nq, d = q.shape
@@ -177,4 +177,4 @@ def run_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool
     _check(fns, fns["prefill"](
         out.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.cu_q.data_ptr() + skip, ctx.q_start.data_ptr() + skip,
         indptr.data_ptr() + skip, indices.data_ptr(), ctx.num_rows - first_row, ctx.max_q_len, nq, nkv, float(scale), int(window or 0),
-        page_size, ctx.stream))
+        int(sink), page_size, ctx.stream))

@@ -1,0 +1,159 @@
+"""Python faces of the kernels in ``csrc/mixer_pointwise.cu`` and ``csrc/recurrence.cu``: Dynamic Tanh,
+tanh-GELU, the general step between a q|k|v projection and attention, gates on attention's output, and
+the linear-attention recurrences with what comes before and after them.
+
+Several operands are column ranges of a wider row (one product makes q, k, v and gates side by side):
+such an operand is passed as a 2-d view whose last stride is 1; its row stride goes to the kernel."""
+
+from __future__ import annotations
+
+import torch
+
+from . import native
+
+
+def _dt(dtype: torch.dtype) -> int:
+    return {torch.float32: 0, torch.bfloat16: 1}[dtype]
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(stream) -> int:
+    return torch.cuda.current_stream().cuda_stream if stream is None else stream
+
+
+def _rows(t: torch.Tensor) -> int:
+    """Row stride of a 2-d operand whose rows are contiguous."""
+    assert t.is_cuda and t.dim() == 2 and (t.stride(1) == 1 or t.shape[1] == 1), "operand rows must be contiguous"
+    return t.stride(0)
+
+
+def _f32(*tensors) -> None:
+    for t in tensors:
+        assert t is None or (t.is_cuda and t.dtype == torch.float32 and t.is_contiguous())
+
+
+def add_dyt(out, residual, delta, weight, bias, alpha, rows=None, num_rows=None, write_residual=True, stream=None) -> None:
+    """out[i] = tanh(alpha * (residual[r] + delta[r])) * weight + bias with r = rows[i] (or i); the sum
+    is written back to ``residual`` when there is no gather. float32 arithmetic, float32 parameters."""
+    _f32(residual, weight, bias, alpha)
+    hidden = residual.shape[-1]
+    n = out.shape[0] if num_rows is None else num_rows
+    assert out.is_contiguous() and out.shape[-1] == hidden and weight.numel() == hidden and bias.numel() == hidden
+    assert delta is None or (delta.dtype == out.dtype and delta.is_contiguous())
+    native.kernel_check(native.kernels().ms_add_dyt(
+        _ptr(out), _ptr(residual), _ptr(delta), _ptr(weight), _ptr(bias), _ptr(alpha), _ptr(rows), n, hidden,
+        int(write_residual and rows is None), _dt(out.dtype), _stream(stream)))
+
+
+def gelu_tanh(out: torch.Tensor, x: torch.Tensor, stream=None) -> None:
+    """out = 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), in float32, rounded once (may be in place)."""
+    assert out.is_contiguous() and x.is_contiguous() and out.dtype == x.dtype and out.numel() == x.numel()
+    native.kernel_check(native.kernels().ms_gelu_tanh(_ptr(out), _ptr(x), x.numel(), _dt(x.dtype), _stream(stream)))
+
+
+def scale_(x: torch.Tensor, s: float, stream=None) -> None:
+    _f32(x)
+    native.kernel_check(native.kernels().ms_scale_f32(_ptr(x), float(s), x.numel(), _stream(stream)))
+
+
+def axpby(out: torch.Tensor, x: torch.Tensor, y: torch.Tensor, a: float, b: float, stream=None) -> None:
+    assert out.is_contiguous() and x.is_contiguous() and y.is_contiguous() and x.dtype == y.dtype == out.dtype
+    assert x.numel() == y.numel() == out.numel()
+    native.kernel_check(native.kernels().ms_axpby(_ptr(out), _ptr(x), _ptr(y), float(a), float(b), x.numel(), _dt(x.dtype),
+                                                  _stream(stream)))
+
+
+def head_gate(out: torch.Tensor, attn: torch.Tensor, gate: torch.Tensor | None, value_dim: int, scale: float, stream=None) -> None:
+    """out[t, h * dv + c] = scale * sigmoid(gate[t, h]) * attn[t, h, c] for c < dv; ``attn`` [T, heads, D],
+    ``out`` and ``gate`` 2-d views of wider rows. Without ``gate`` only the scale and the cut to dv remain."""
+    t, nq, d = attn.shape
+    assert attn.is_contiguous() and out.shape == (t, nq * value_dim) and out.dtype == attn.dtype
+    assert gate is None or (gate.shape == (t, nq) and gate.dtype == attn.dtype)
+    native.kernel_check(native.kernels().ms_head_gate(
+        _ptr(out), _rows(out), _ptr(attn), _ptr(gate), 0 if gate is None else _rows(gate), t, nq, d, value_dim, float(scale),
+        _dt(attn.dtype), _stream(stream)))
+
+
+def qkv_prepare(q_out, k_pool, v_pool, q, k, v, q_norm_w, k_norm_w, cos_sin, rotary_dim: int, adjacent: bool, eps: float,
+                positions, row_of_token, page_indptr, page_indices, page_size: int, status, stream=None) -> None:
+    """Per-head RMS norm of q and k (float32 weights or None), rotation of the first ``rotary_dim`` channels
+    (pairs (2i, 2i+1) if ``adjacent`` else (i, i + rotary_dim/2)) by the step's cos/sin table, q to
+    ``q_out`` [T, nq, D] and k, v into their pages [pages, nkv, page_size, D], zero beyond their own
+    sizes. ``q`` [T, nq*dk], ``k`` [T, nkv*dk], ``v`` [T, nkv*dv]: views into one projection's rows."""
+    t, nq, d = q_out.shape
+    nkv = k_pool.shape[1]
+    dk, dv = q.shape[1] // nq, v.shape[1] // nkv
+    assert k.shape == (t, nkv * dk) and q.shape == (t, nq * dk) and v.shape == (t, nkv * dv)
+    assert k_pool.shape == v_pool.shape and k_pool.shape[2] == page_size and k_pool.shape[3] == d
+    assert q.dtype == k.dtype == v.dtype == q_out.dtype == k_pool.dtype
+    ld = _rows(q)
+    assert _rows(k) == ld and _rows(v) == ld, "q, k and v must be columns of the same rows"
+    item = q.element_size()
+    base = min(q.data_ptr(), k.data_ptr(), v.data_ptr())
+    offs = [(x.data_ptr() - base) // item for x in (q, k, v)]
+    _f32(q_norm_w, k_norm_w, cos_sin)
+    assert cos_sin is None or cos_sin.shape == (t, rotary_dim)
+    native.kernel_check(native.kernels().ms_qkv_prepare(
+        _ptr(q_out), _ptr(k_pool), _ptr(v_pool), base, ld, offs[0], offs[1], offs[2], _ptr(q_norm_w), _ptr(k_norm_w),
+        _ptr(cos_sin), _ptr(positions), _ptr(row_of_token), _ptr(page_indptr), _ptr(page_indices), t, nq, nkv, dk, dv, d,
+        rotary_dim if cos_sin is not None else 0, int(adjacent), float(eps), page_size, k_pool.shape[0], _ptr(status),
+        _dt(q.dtype), _stream(stream)))
+
+
+def decay_scan(o_out, state, q, k, v, z, z_bias, decay_coef, z_sign: float, beta, ctx, heads: int, dk: int, dv: int,
+               q_scale: float, delta: bool) -> None:
+    """The token-by-token recurrence of every row of the step (``csrc/recurrence.cu``), from each
+    request's slot of ``state`` [slots, heads, dv, dk] float32 (zero where a row starts at position 0)
+    and back into it; o_out [T, heads, dv] float32. q, k [T, groups*dk], v [T, heads*dv], z [T, heads*dk]
+    and beta [T, heads] are 2-d views; z_bias [heads*dk], decay_coef [heads] float32."""
+    t = o_out.shape[0]
+    _f32(o_out, state, z_bias, decay_coef)
+    assert o_out.shape == (t, heads, dv) and state.shape[1:] == (heads, dv, dk)
+    groups = q.shape[1] // dk
+    assert q.shape == (t, groups * dk) and k.shape == q.shape and v.shape == (t, heads * dv) and z.shape == (t, heads * dk)
+    assert q.dtype == k.dtype == v.dtype and (beta is None or beta.dtype == z.dtype)
+    native.kernel_check(native.kernels().ms_decay_scan(
+        _ptr(o_out), _ptr(state), _ptr(q), _rows(q), _ptr(k), _rows(k), heads // groups, _ptr(v), _rows(v), _ptr(z), _rows(z),
+        _ptr(z_bias), _ptr(decay_coef), float(z_sign), _ptr(beta), 0 if beta is None else _rows(beta), _ptr(ctx.cu_q),
+        _ptr(ctx.q_start), _ptr(ctx.state_slot), ctx.num_rows, heads, dk, dv, float(q_scale), int(delta), _dt(q.dtype),
+        _dt(z.dtype), ctx.stream))
+
+
+def conv_silu_unit(out, x, conv_state, weight, ctx, unit_heads: int, dk: int, other_heads: int, dv: int, unit_eps: float) -> None:
+    """out [T, C] float32 = SiLU(causal convolution over time of the C channels ``x`` [T, C], a view),
+    the first ``unit_heads`` heads of dk channels then divided by sqrt(sum of squares + unit_eps).
+    ``weight`` [C, taps] float32; ``conv_state`` [slots, taps - 1, C] holds each request's last inputs."""
+    t, c = out.shape
+    taps = weight.shape[1]
+    _f32(out, weight)
+    assert x.shape == (t, c) and weight.shape[0] == c and conv_state.dtype == x.dtype and conv_state.is_contiguous()
+    assert conv_state.shape[1:] == (max(taps - 1, 0), c)
+    native.kernel_check(native.kernels().ms_conv_silu_unit(
+        _ptr(out), _ptr(x), _rows(x), _ptr(conv_state), _ptr(weight), _ptr(ctx.row_of_token), _ptr(ctx.cu_q), _ptr(ctx.q_start),
+        _ptr(ctx.state_slot), t, c, taps, unit_heads, dk, other_heads, dv, float(unit_eps), _dt(x.dtype), ctx.stream))
+
+
+def conv_state_update(conv_state, x, ctx, taps: int) -> None:
+    """Each row's slot of ``conv_state`` [slots, taps - 1, C] becomes the last taps - 1 inputs ``x`` [T, C]
+    of its sequence after this step (older entries move up when the portion is shorter than that)."""
+    assert conv_state.dtype == x.dtype and conv_state.is_contiguous()
+    native.kernel_check(native.kernels().ms_conv_state_update(
+        _ptr(conv_state), _ptr(x), _rows(x), _ptr(ctx.cu_q), _ptr(ctx.q_start), _ptr(ctx.state_slot), ctx.num_rows, x.shape[1],
+        taps, _dt(x.dtype), ctx.stream))
+
+
+GATE_KINDS = {"silu": 0, "sigmoid": 1}
+
+
+def head_norm_gate(out, o, weight, gate, eps: float, scale: float, gate_kind: str, stream=None) -> None:
+    """out[t, h*dv + c] = scale * o[t, h, c] / sqrt(mean_c o^2 + eps) * weight[c] * act(gate[t, h*dv + c]);
+    ``o`` [T, heads, dv] float32, ``out`` and ``gate`` 2-d views, act SiLU or sigmoid."""
+    t, heads, dv = o.shape
+    _f32(o, weight)
+    assert out.shape == (t, heads * dv) and gate.shape == (t, heads * dv) and gate.dtype == out.dtype and weight.numel() == dv
+    native.kernel_check(native.kernels().ms_head_norm_gate(
+        _ptr(out), _rows(out), _ptr(o), _ptr(weight), _ptr(gate), _rows(gate), t, heads, dv, float(eps), float(scale),
+        GATE_KINDS[gate_kind], _dt(out.dtype), _stream(stream)))

@@ -108,7 +108,18 @@ def kernels():
     _declare(lib, "ms_rope_table_tile", [_p, _p, _i, _p])
     _declare(lib, "ms_gemm_f32", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p])
     _declare(lib, "ms_attention_rowwise",
-             [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _i, _p, _i, _p])
+             [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p, _i, _p])
+    _declare(lib, "ms_add_dyt", [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_gelu_tanh", [_p, _p, _ll, _i, _p])
+    _declare(lib, "ms_scale_f32", [_p, _f, _ll, _p])
+    _declare(lib, "ms_axpby", [_p, _p, _p, _f, _f, _ll, _i, _p])
+    _declare(lib, "ms_head_gate", [_p, _i, _p, _p, _i, _i, _i, _i, _i, _f, _i, _p])
+    _declare(lib, "ms_qkv_prepare", [_p] * 4 + [_i] * 4 + [_p] * 7 + [_i] * 8 + [_f, _i, _i, _p, _i, _p])
+    _declare(lib, "ms_decay_scan", [_p, _p, _p, _i, _p, _i, _i, _p, _i, _p, _i, _p, _p, _f, _p, _i, _p, _p, _p,
+                                    _i, _i, _i, _i, _f, _i, _i, _i, _p])
+    _declare(lib, "ms_conv_silu_unit", [_p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p])
+    _declare(lib, "ms_conv_state_update", [_p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_head_norm_gate", [_p, _i, _p, _p, _p, _i, _i, _i, _i, _f, _f, _i, _i, _p])
     _declare(lib, "ms_nucleus_bytes", [])
     _declare(lib, "ms_sample_scratch_bytes", [_i, _i], _ll)
     _declare(lib, "ms_sample", [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p])
@@ -137,7 +148,7 @@ def attn_tc():
     _declare(lib, "ms_attn_tc_supports", [_i, _i, _i, _i])
     _declare(lib, "ms_attn_tc_plan", [_p, _p, _i, _i, _i, _i, _i, _p, _p], None)
     _declare(lib, "ms_attn_tc_scratch", [_i, _i, _i, _i, _i, _p, _p], None)
-    _declare(lib, "ms_attn_tc_prefill", [_p] * 8 + [_i, _i, _i, _i, _i, _ll, _f, _i, _i, _p, _i, _i, _p, _p, _p, _p])
+    _declare(lib, "ms_attn_tc_prefill", [_p] * 8 + [_i, _i, _i, _i, _i, _ll, _f, _i, _i, _i, _p, _i, _i, _p, _p, _p, _p])
     _declare(lib, "ms_attn_tc_write_plan", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _ll, _ll, _p])
     lib.ms_attn_tc_set_pdl(int(pdl_enabled()))
     return lib

@@ -19,8 +19,21 @@ class GQAttention(Part):
     ``qk_norm_eps``, ``position`` (a PartSpec of category ``position``), optional ``window``
     (a query sees only the last ``window`` keys), optional ``scale``, and ``kv_source``:
     ``own`` (default) or ``shared`` (the layer has no k/v projections and attends over the
-    cache of the run entry named by ``RunEntry.cache_of``)."""
+    cache of the run entry named by ``RunEntry.cache_of``).
+
+    Further optional parameters, for designs that are not Qwen3's: ``sink`` (the softmax's denominator
+    has one more term of score 0, which carries no value: weights exp(s_j) / (1 + sum exp(s))),
+    ``value_dim`` (a value size other than the key size ``head_dim``), ``out_gate`` = ``head_sigmoid``
+    (head h's output is multiplied by sigmoid(W_g x)_h, one number per token and head, before the output
+    projection), a position encoding that pairs adjacent channels (``rope_pairs``), and ``names`` (the
+    tensors' names: q, k, v, o, q_norm, k_norm, gate). A gate, another value size or adjacent pairing
+    take the general kernels: one product makes q|k|v|gate, ``ops.qkv_prepare`` norms and rotates in
+    float32 and writes keys and values padded with zeros to one cache head size (a zero channel changes
+    no score and no output), and ``ops.head_gate`` cuts, gates and scales attention's output.
+    ``features`` stops before the output projection, for a mixer that joins several branches in one."""
     shape_static = True
+    NAMES = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight", q_norm="q_norm.weight",
+                 k_norm="k_norm.weight", gate="g_proj.weight")
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -41,6 +54,18 @@ class GQAttention(Part):
             raise ValueError(f"window must be positive, got {self.window}")
         pos_spec = spec.get("position") or PartSpec("none")
         self.position = build_part("position", pos_spec, env)
+        self.sink = bool(spec.get("sink", False))
+        self.value_dim = int(spec.get("value_dim") or self.head_dim)
+        self.out_gate = spec.get("out_gate")
+        if self.out_gate not in (None, "head_sigmoid"):
+            raise ValueError(f"out_gate must be 'head_sigmoid' or absent, got {self.out_gate!r}")
+        self.names = {**self.NAMES, **dict(spec.get("names") or {})}
+        self.general = bool(self.out_gate or self.value_dim != self.head_dim or self.position.pairing == "adjacent")
+        if self.general and not self.owns_cache:
+            raise ValueError("a gate, a value size of its own or adjacent rotation pairs need a cache of the mixer's own")
+        # the general path keeps keys and values in one head size: the larger of the two, in steps of 16
+        self.cache_dim = -(-max(self.head_dim, self.value_dim) // 16) * 16 if self.general else self.head_dim
+        self.feature_width = self.heads * self.value_dim
 
     @property
     def owns_cache(self) -> bool:
@@ -49,38 +74,74 @@ class GQAttention(Part):
     def cache_need(self):
         if not self.owns_cache:
             return None
-        return PagedKV(self.kv_heads, self.head_dim, int(self.window) if self.window else None)
+        return PagedKV(self.kv_heads, self.cache_dim, int(self.window) if self.window else None)
 
     def weights(self):
-        d = self.head_dim
-        w = {"q_proj.weight": WeightDecl((self.heads * d, self.hidden)),
-             "o_proj.weight": WeightDecl((self.hidden, self.heads * d))}
+        d, n = self.head_dim, self.names
+        w = {n["q"]: WeightDecl((self.heads * d, self.hidden)),
+             n["o"]: WeightDecl((self.hidden, self.heads * self.value_dim))}
         if self.owns_cache:
-            w["k_proj.weight"] = WeightDecl((self.kv_heads * d, self.hidden))
-            w["v_proj.weight"] = WeightDecl((self.kv_heads * d, self.hidden))
+            w[n["k"]] = WeightDecl((self.kv_heads * d, self.hidden))
+            w[n["v"]] = WeightDecl((self.kv_heads * self.value_dim, self.hidden))
+        if self.out_gate:
+            w[n["gate"]] = WeightDecl((self.heads, self.hidden))
         if self.qk_norm:
-            w["q_norm.weight"] = WeightDecl((d,), init="ones_normal")
+            # the general kernel takes the norm's weights in float32, the others in the run's dtype
+            kind = dict(precision="float32") if self.general else {}
+            w[n["q_norm"]] = WeightDecl((d,), init="ones_normal", **kind)
             if self.owns_cache:
-                w["k_norm.weight"] = WeightDecl((d,), init="ones_normal")
+                w[n["k_norm"]] = WeightDecl((d,), init="ones_normal", **kind)
         return w
 
+    def _stack(self) -> tuple[str, tuple[str, ...]]:
+        n = self.names
+        return "qkv_proj.weight", (n["q"], n["k"], n["v"]) + ((n["gate"],) if self.out_gate else ())
+
     def stacks(self):
-        # one product makes q, k and v (miniserve/model/fused.py:41-95 joins the same rows)
-        return {"qkv_proj.weight": ("q_proj.weight", "k_proj.weight", "v_proj.weight")} if self.owns_cache else {}
+        # one product makes q, k and v (miniserve/model/fused.py:41-95 joins the same rows), and the gate
+        return dict([self._stack()]) if self.owns_cache else {}
 
     def bind(self, tensors):
+        n = self.names
         if self.owns_cache:
-            self.w_qkv = self.joined(tensors, "qkv_proj.weight", self.stacks()["qkv_proj.weight"])
+            self.w_qkv = self.joined(tensors, *self._stack())
+            if self.general and self.w_qkv.shape[0] % 8:
+                # rows of the product's output start on 16 bytes: a few zero rows at the end
+                pad = torch.zeros((-self.w_qkv.shape[0] % 8, self.hidden), dtype=self.w_qkv.dtype, device=self.w_qkv.device)
+                self.w_qkv = torch.cat((self.w_qkv, pad), dim=0).contiguous()
         else:
-            self.w_qkv = tensors["q_proj.weight"].contiguous()
-        self.w_o = tensors["o_proj.weight"].contiguous()
-        self.w_q_norm = tensors["q_norm.weight"].contiguous() if self.qk_norm else None
-        self.w_k_norm = tensors["k_norm.weight"].contiguous() if self.qk_norm and self.owns_cache else None
+            self.w_qkv = tensors[n["q"]].contiguous()
+        self.w_o = tensors[n["o"]].contiguous()
+        self.w_q_norm = tensors[n["q_norm"]].contiguous() if self.qk_norm else None
+        self.w_k_norm = tensors[n["k_norm"]].contiguous() if self.qk_norm and self.owns_cache else None
+
+    def features(self, x: torch.Tensor, ctx, cache, out: torch.Tensor, scale: float = 1.0) -> None:
+        """The general path up to the output projection's input: ``out`` [T, heads * value_dim] (a view
+        whose rows may be part of wider ones) = scale * gate * attention."""
+        t = x.shape[0]
+        dt, dev = self.env.dtype, self.w_qkv.device
+        nq, nkv, dk, dv, dc = self.heads, self.kv_heads, self.head_dim, self.value_dim, self.cache_dim
+        proj = ops.linear(x, self.w_qkv, stream=ctx.stream, out=ctx.buffer("attn.qkv", (t, self.w_qkv.shape[0]), dt, dev))
+        at_k, at_v, at_g = nq * dk, (nq + nkv) * dk, (nq + nkv) * dk + nkv * dv
+        q = ctx.buffer("attn.q", (t, nq, dc), dt, dev)
+        _, rotary_dim = self.position.kernel_table()
+        ops.qkv_prepare(q, cache.k, cache.v, proj[:, :at_k], proj[:, at_k:at_v], proj[:, at_v:at_g], self.w_q_norm, self.w_k_norm,
+                        self.position.step_table(ctx), rotary_dim, self.position.pairing == "adjacent", self.qk_norm_eps,
+                        ctx.positions, ctx.row_of_token, ctx.page_indptr[cache.group], ctx.page_indices[cache.group],
+                        cache.page_size, ctx.status, stream=ctx.stream)
+        att = ctx.buffer("attn.out", (t, nq, dc), dt, dev)
+        ops.attention(att, q, cache.k, cache.v, ctx, cache.group, self.scale, self.window, self.sink)
+        gate = proj[:, at_g:at_g + nq] if self.out_gate else None
+        ops.head_gate(out, att, gate, dv, scale, stream=ctx.stream)
 
     def forward(self, x: torch.Tensor, ctx, cache):
         """Returns the mixer's addend to the residual stream: a tensor [T, hidden]."""
         t = x.shape[0]
         dt, dev = self.env.dtype, self.w_qkv.device
+        if self.general:
+            feat = ctx.buffer("attn.feat", (t, self.feature_width), dt, dev)
+            self.features(x, ctx, cache, feat)
+            return ops.linear(feat, self.w_o, stream=ctx.stream, out=ctx.buffer("attn.proj", (t, self.w_o.shape[0]), dt, dev))
         q = ctx.buffer("attn.q", (t, self.heads, self.head_dim), dt, dev)
         inv_freq, rotary_dim = self.position.kernel_table()
         indptr, indices = ctx.page_indptr[cache.group], ctx.page_indices[cache.group]
@@ -105,6 +166,6 @@ class GQAttention(Part):
                 ctx.row_of_token, indptr, indices, cache.page_size, ctx.status, stream=ctx.stream,
                 cos_sin=self.position.step_table(ctx))
         out = ctx.buffer("attn.out", (t, self.heads, self.head_dim), dt, dev)
-        ops.attention(out, q, cache.k, cache.v, ctx, cache.group, self.scale, self.window)
+        ops.attention(out, q, cache.k, cache.v, ctx, cache.group, self.scale, self.window, self.sink)
         return ops.linear(out.view(t, self.heads * self.head_dim), self.w_o, stream=ctx.stream,
                           out=ctx.buffer("attn.proj", (t, self.w_o.shape[0]), dt, dev))

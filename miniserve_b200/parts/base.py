@@ -10,7 +10,8 @@ Categories and what each must provide:
 
 ``norm``          ``forward(residual, delta, ctx, rows=None, write_residual=True) -> Tensor``
 ``position``      ``kernel_table() -> (inv_freq | None, rotary_dim)``, ``step_table(ctx) -> cos/sin table | None``
-``mixer``         ``cache_need() -> CacheNeed | None`` and ``forward(x, ctx, cache) -> Tensor``
+``mixer``         ``cache_need() -> CacheNeed | tuple of them | None`` and ``forward(x, ctx, cache) -> Tensor``
+                  (``cache``: the view of its need, or a tuple of views in the order of the needs)
 ``feed_forward``  ``forward(x, ctx) -> Tensor``
 ``block``         ``forward(stream, ctx, cache) -> ResidualStream`` (arranges the four above)
 ``embedding``     ``forward(ctx) -> float32 residual [T, hidden]``
@@ -93,6 +94,15 @@ class FixedState:
 
 
 CacheNeed = PagedKV | FixedState
+
+
+def flat_needs(need) -> tuple:
+    """The single needs inside what a mixer's ``cache_need`` returned (None, one need, or nested tuples)."""
+    if need is None:
+        return ()
+    if isinstance(need, (PagedKV, FixedState)):
+        return (need,)
+    return tuple(n for part in need for n in flat_needs(part))
 
 
 class Part:

@@ -11,7 +11,8 @@ class PreNormBlock(Part):
     """h += mixer(norm1(h)); h += feed_forward(norm2(h)) (miniserve/model/qwen3.py:212-216).
     The adds are fused into the norm that follows them, so the block hands its last addend
     on as ``pending``. Parameters: ``names`` maps mixer / feed_forward / norm1 / norm2 to their
-    tensor-name prefixes inside the layer."""
+    tensor-name prefixes inside the layer. A layer without a feed-forward (``LayerSpec.feed_forward`` None)
+    has neither it nor norm2, and hands the mixer's output on as the pending addend."""
     shape_static = True
 
     def __init__(self, spec, env: BuildEnv, layer: LayerSpec | None = None):
@@ -19,20 +20,25 @@ class PreNormBlock(Part):
         if layer is None:
             raise ValueError("a block is built from its LayerSpec (use build_block)")
         names = dict(spec.get("names") or {})
-        self.names = {k: names[k] for k in ("mixer", "feed_forward", "norm1", "norm2")}
+        self.has_ff = layer.feed_forward is not None
+        self.names = {k: names[k] for k in ("mixer", "norm1") + (("feed_forward", "norm2") if self.has_ff else ())}
         self.mixer = build_part("mixer", layer.mixer, env)
-        self.feed_forward = build_part("feed_forward", layer.feed_forward, env)
         self.norm1 = build_part("norm", layer.norms["norm1"], env)
-        self.norm2 = build_part("norm", layer.norms["norm2"], env)
+        self.feed_forward = build_part("feed_forward", layer.feed_forward, env) if self.has_ff else None
+        self.norm2 = build_part("norm", layer.norms["norm2"], env) if self.has_ff else None
 
     def sub_parts(self):
-        return {self.names["mixer"]: self.mixer, self.names["feed_forward"]: self.feed_forward,
-                self.names["norm1"]: self.norm1, self.names["norm2"]: self.norm2}
+        out = {self.names["mixer"]: self.mixer, self.names["norm1"]: self.norm1}
+        if self.has_ff:
+            out.update({self.names["feed_forward"]: self.feed_forward, self.names["norm2"]: self.norm2})
+        return out
 
     def forward(self, stream: ResidualStream, ctx, cache) -> ResidualStream:
         total = stream.total
         x = self.norm1.forward(total, stream.pending, ctx)
         a = self.mixer.forward(x, ctx, cache)
+        if not self.has_ff:
+            return ResidualStream(total, a)
         x = self.norm2.forward(total, a, ctx)
         return ResidualStream(total, self.feed_forward.forward(x, ctx))
 

@@ -19,7 +19,7 @@ class EntryCache:
     unless the entry reads another's), ``need`` what that owner asked for."""
 
     owner: int
-    need: CacheNeed | None
+    need: "CacheNeed | tuple | None"  # one need, or a tuple of needs (a mixer made of several)
 
 
 class DecoderModel:

@@ -38,7 +38,7 @@ class LinearHead(Part):
     """logits = x @ W^T, no bias (miniserve/model/qwen3.py:186); with ``tied`` the matrix is the
     embedding table itself and no tensor of its own is read (miniserve/model/weights.py:116-119,
     135-136). Logits are returned in float32. Parameters: ``vocab``, ``hidden``, ``tied``,
-    ``name``, ``tied_to``."""
+    ``name``, ``tied_to``, optional ``scale`` (the float32 logits are multiplied by it)."""
     shape_static = True
 
     def __init__(self, spec, env):
@@ -48,6 +48,7 @@ class LinearHead(Part):
         self.tied = bool(spec.get("tied", False))
         self.name = param(spec, "name", str)
         self.tied_to = spec.get("tied_to")
+        self.scale = float(spec.get("scale") or 1.0)
         if self.tied and not self.tied_to:
             raise ValueError("a tied head needs 'tied_to', the name of the embedding tensor")
 
@@ -62,4 +63,6 @@ class LinearHead(Part):
         logits = torch.empty((x.shape[0], self.vocab), dtype=torch.float32, device=x.device)
         if x.shape[0]:
             ops.linear(x, self.weight, out=logits, stream=ctx.stream)
+            if self.scale != 1.0:
+                ops.scale_(logits, self.scale, stream=ctx.stream)
         return logits

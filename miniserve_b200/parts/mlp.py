@@ -46,3 +46,34 @@ class SwiGLU(Part):
             gate_up = ops.linear(x, self.w_gate_up, stream=ctx.stream, out=ctx.buffer("mlp.gate_up", (t, 2 * self.inter), dt, dev))
             ops.silu_mul(act, gate_up, stream=ctx.stream)
         return ops.linear(act, self.w_down, stream=ctx.stream, out=ctx.buffer("mlp.down", (t, self.hidden), dt, dev))
+
+
+@register_part("feed_forward", "dense_mlp")
+class DenseMLP(Part):
+    """down(act(up(x))), no gate and no biases. Parameters: ``hidden``, ``intermediate``, ``activation``
+    (``gelu_tanh``: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))), ``names`` (up / down -> tensor names)."""
+    shape_static = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = param(spec, "hidden", int)
+        self.inter = param(spec, "intermediate", int)
+        self.activation = spec.get("activation", "gelu_tanh")
+        if self.activation != "gelu_tanh":
+            raise ValueError(f"dense_mlp knows the activation 'gelu_tanh', not {self.activation!r}")
+        names = dict(spec.get("names") or {})
+        self.names = {"up": names.get("up", "up_proj.weight"), "down": names.get("down", "down_proj.weight")}
+
+    def weights(self):
+        return {self.names["up"]: WeightDecl((self.inter, self.hidden)),
+                self.names["down"]: WeightDecl((self.hidden, self.inter))}
+
+    def bind(self, tensors):
+        self.w_up = tensors[self.names["up"]].contiguous()
+        self.w_down = tensors[self.names["down"]].contiguous()
+
+    def forward(self, x, ctx) -> torch.Tensor:
+        t, dt, dev = x.shape[0], self.env.dtype, self.w_down.device
+        act = ops.linear(x, self.w_up, stream=ctx.stream, out=ctx.buffer("mlp.act", (t, self.inter), dt, dev))
+        ops.gelu_tanh(act, act, stream=ctx.stream)
+        return ops.linear(act, self.w_down, stream=ctx.stream, out=ctx.buffer("mlp.down", (t, self.hidden), dt, dev))

@@ -31,3 +31,38 @@ class RMSNorm(Part):
         ops.add_rmsnorm(out, residual, delta, self.w_weight, self.eps, rows=rows, num_rows=n,
                         write_residual=write_residual, stream=ctx.stream)
         return out
+
+
+@register_part("norm", "dynamic_tanh")
+class DynamicTanh(Part):
+    """y = tanh(alpha x) * weight + bias in the place of a norm: no mean, no variance, so no reduction
+    over the row; alpha is one learned scalar. Computed in float32 from float32 parameters, with the
+    residual add fused in as for RMSNorm. Parameters: ``size``; ``names`` maps weight / bias / alpha to
+    tensor names relative to the part's prefix (default ``weight``, ``bias``, ``alpha``)."""
+    shape_static = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.size = param(spec, "size", int)
+        names = dict(spec.get("names") or {})
+        self.names = {k: names.get(k, k) for k in ("weight", "bias", "alpha")}
+
+    def weights(self):
+        n = self.names
+        return {n["weight"]: WeightDecl((self.size,), precision="float32", init="ones_normal"),
+                n["bias"]: WeightDecl((self.size,), precision="float32"),
+                n["alpha"]: WeightDecl((), precision="float32", init="ones_normal")}
+
+    def bind(self, tensors):
+        n = self.names
+        self.w_weight = tensors[n["weight"]].contiguous()
+        self.w_bias = tensors[n["bias"]].contiguous()
+        self.w_alpha = tensors[n["alpha"]].reshape(1).contiguous()
+
+    def forward(self, residual: torch.Tensor, delta: torch.Tensor | None, ctx, rows: torch.Tensor | None = None,
+                num_rows: int | None = None, write_residual: bool = True) -> torch.Tensor:
+        n = residual.shape[0] if rows is None else (num_rows if num_rows is not None else rows.numel())
+        out = ctx.buffer("norm.out", (n, self.size), self.env.dtype, residual.device)
+        ops.add_dyt(out, residual, delta, self.w_weight, self.w_bias, self.w_alpha, rows=rows, num_rows=n,
+                    write_residual=write_residual, stream=ctx.stream)
+        return out

@@ -55,7 +55,7 @@ def test_decode_without_allocation_matches_the_allocating_entry_point(nq, nkv, d
     expect = torch.full_like(q, float("nan"))
     rc = fns["decode"](expect.data_ptr(), part_o.data_ptr(), part_ml.data_ptr(), q.data_ptr(), pb.k_pool.data_ptr(),
                        pb.v_pool.data_ptr(), pb.kv_len.data_ptr(), pb.page_indptr.data_ptr(), pb.page_indices.data_ptr(),
-                       len(rows), nq, nkv, scale, 0, page, splits, stream)
+                       len(rows), nq, nkv, scale, 0, 0, page, splits, stream)
     assert rc == 0
     assert torch.allclose(expect.float(), ref, atol=2e-2, rtol=2e-2)
 
