@@ -92,28 +92,32 @@ decay_scan_kernel(float* __restrict__ o_out,   // [T, H, dv]
       const float* kt = ks + tt * dkp + l * (SCAN_KPT + 1);
       const float* dt = ds + tt * dkp + l * (SCAN_KPT + 1);
       const float vj = vs[tt * cols + col];
-      float acc = 0.f;
+      // sums over a thread's channels in four interleaved chains (a fixed order), so that the token's
+      // critical path is four products deep and not sixteen
+      float a4[4] = {0.f, 0.f, 0.f, 0.f};
       if (DELTA) {
-        float dot = 0.f;
+        float d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int e = 0; e < SCAN_KPT; ++e) {
           S[e] *= dt[e];
-          dot = fmaf(kt[e], S[e], dot);
+          d4[e & 3] = fmaf(kt[e], S[e], d4[e & 3]);
         }
+        float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
         for (int off = L >> 1; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
         const float u = bs[tt] * (vj - dot);
 #pragma unroll
         for (int e = 0; e < SCAN_KPT; ++e) {
           S[e] = fmaf(kt[e], u, S[e]);
-          acc = fmaf(qt[e], S[e], acc);
+          a4[e & 3] = fmaf(qt[e], S[e], a4[e & 3]);
         }
       } else {
 #pragma unroll
         for (int e = 0; e < SCAN_KPT; ++e) {
           S[e] = fmaf(dt[e], S[e], kt[e] * vj);
-          acc = fmaf(qt[e], S[e], acc);
+          a4[e & 3] = fmaf(qt[e], S[e], a4[e & 3]);
         }
       }
+      float acc = (a4[0] + a4[1]) + (a4[2] + a4[3]);
       for (int off = L >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
       if (l == 0 && active) o_out[((size_t)(c0 + tt) * H + h) * dv + j] = acc;
     }

@@ -60,7 +60,8 @@ class GQAttention(Part):
         if self.out_gate not in (None, "head_sigmoid"):
             raise ValueError(f"out_gate must be 'head_sigmoid' or absent, got {self.out_gate!r}")
         self.names = {**self.NAMES, **dict(spec.get("names") or {})}
-        self.general = bool(self.out_gate or self.value_dim != self.head_dim or self.position.pairing == "adjacent")
+        self.adjacent = getattr(self.position, "pairing", "halves") == "adjacent"  # how the position encoding pairs channels
+        self.general = bool(self.out_gate or self.value_dim != self.head_dim or self.adjacent)
         if self.general and not self.owns_cache:
             raise ValueError("a gate, a value size of its own or adjacent rotation pairs need a cache of the mixer's own")
         # the general path keeps keys and values in one head size: the larger of the two, in steps of 16
@@ -126,7 +127,7 @@ class GQAttention(Part):
         q = ctx.buffer("attn.q", (t, nq, dc), dt, dev)
         _, rotary_dim = self.position.kernel_table()
         ops.qkv_prepare(q, cache.k, cache.v, proj[:, :at_k], proj[:, at_k:at_v], proj[:, at_v:at_g], self.w_q_norm, self.w_k_norm,
-                        self.position.step_table(ctx), rotary_dim, self.position.pairing == "adjacent", self.qk_norm_eps,
+                        self.position.step_table(ctx), rotary_dim, self.adjacent, self.qk_norm_eps,
                         ctx.positions, ctx.row_of_token, ctx.page_indptr[cache.group], ctx.page_indices[cache.group],
                         cache.page_size, ctx.status, stream=ctx.stream)
         att = ctx.buffer("attn.out", (t, nq, dc), dt, dev)

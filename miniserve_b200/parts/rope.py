@@ -20,7 +20,8 @@ class RotaryNeox(Part):
         super().__init__(spec, env)
         self.head_dim = param(spec, "head_dim", int)
         self.theta = param(spec, "theta", float)
-        self.rotary_dim = int(spec.get("rotary_dim") or self.head_dim)
+        rotary = spec.get("rotary_dim")
+        self.rotary_dim = self.head_dim if rotary is None else int(rotary)  # 0: nothing is rotated
         if self.rotary_dim % 2 or self.rotary_dim > self.head_dim:
             raise ValueError(f"rotary_dim={self.rotary_dim} must be even and at most head_dim={self.head_dim}")
         self.inv_freq = self._frequencies().to(env.device)
@@ -39,6 +40,8 @@ class RotaryNeox(Part):
         from .. import ops
 
         key = ("rope_table", type(self).__name__, self.theta, self.rotary_dim)
+        if self.rotary_dim == 0:
+            return None
         table = ctx.step_cache.get(key)
         if table is None:
             table = ops.rope_table(ctx.positions, self.inv_freq, ctx.num_tokens, self.rotary_dim, stream=ctx.stream)

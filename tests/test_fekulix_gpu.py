@@ -48,6 +48,12 @@ def _bind(part, dtype, seed=0, std=0.3):
     return {k: v.double().cpu() for k, v in tensors.items()}
 
 
+@pytest.fixture(autouse=True)
+def _seeded():
+    torch.manual_seed(1234)
+    torch.cuda.manual_seed(1234)
+
+
 def _ctx(rows, page=8, kv_heads=1, d=16, dtype=torch.float32, slots=None, share=None, seed=0):
     pb = PagedBatch(rows, page, kv_heads, d, dtype, seed=seed, share=share)
     ctx = make_context(pb)
