@@ -17,6 +17,11 @@ requests with prompts of 128 to 4,096 tokens and 128 output tokens; Qwen3-32B sh
 with 8,192-token prompts and 128 output tokens, in a pool too small for all of them) through
 ``Engine.generate`` and print one line with tokens per second, the mean time of decode and of
 mixed steps, their fraction of the measured peaks, and the number of preemptions.
+
+``--config fekulix`` measures the Fekulix design (random weights, the layer sizes of Qwen3-0.6B and
+Qwen3-1.7B) beside the Qwen3 model of the same width, depth, feed-forward size and vocabulary: one
+2,048-token prompt step and decode steps at batch 8 behind 2,048 tokens; ``--kernels`` adds the device
+time per kernel of both steps.
 """
 
 from __future__ import annotations
@@ -331,6 +336,102 @@ def run_ours(args) -> dict:
     }
 
 
+# ------------------------------------------------------------------ --config fekulix
+def fekulix_config(width: int, ff: int, runs: int, vocab: int, heads: int, kv_heads: int) -> dict:
+    """A Fekulix model at a real model's layer sizes: three parallel layers (softmax attention with the
+    heads of the Qwen3 model of this width beside linear attention) to one channel_delta layer."""
+    left = {"dim": 128, "heads": heads, "kv_heads": kv_heads, "rot": {"base": 1e6, "dims": 64}, "scale": 128 ** -0.5, "vdim": 128}
+    right = {"dim": 64, "heads": width // 128, "tau": 16.0, "vdim": 128, "decay_rank": 64}
+    par = {"type": "parallel", "mixer": {"left": left, "left_scale": 1.0, "right": right, "right_scale": 1.0},
+           "mlp": {"ff": ff, "kind": "dense"}}
+    delta = {"type": "channel_delta", "mlp": {"ff": ff, "kind": "dense"},
+             "mixer": {"conv": 4, "dim": 64, "heads": width // 64, "kv_heads": width // 128, "vdim": 64, "decay_rank": 64, "gate_rank": 64}}
+    return {"architecture": "Fekulix", "width": width, "vocab": vocab, "logit_scale": 1.0, "norm": {"eps": 1e-6},
+            "layers": [delta if i % 4 == 3 else par for i in range(runs)]}
+
+
+def kernel_times(run_step, repeats: int = 3) -> dict:
+    """Device time per kernel name (us per step, launches per step) of ``run_step()``, from the activity
+    records of torch.profiler (no counters, nothing is replayed); {} if the records cannot be had."""
+    import torch
+
+    try:
+        from torch.profiler import ProfilerActivity, profile
+
+        run_step()
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(repeats):
+                run_step()
+            torch.cuda.synchronize()
+        out = {}
+        for ev in prof.key_averages():
+            us = getattr(ev, "device_time_total", None) or getattr(ev, "cuda_time_total", 0.0)
+            if us and ev.count:
+                name = ev.key.split("<")[0].split("(")[0].replace("void ", "").replace("ms::", "")
+                slot = out.setdefault(name, [0.0, 0.0])
+                slot[0] += us / repeats
+                slot[1] += ev.count / repeats
+        top = sorted(out.items(), key=lambda kv: -kv[1][0])[:14]
+        return {k: {"us_per_step": round(v[0], 1), "launches_per_step": round(v[1], 1)} for k, v in top}
+    except Exception as e:  # noqa: BLE001 (a box without activity tracing still gives the totals)
+        return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+
+
+def run_fekulix(args) -> dict:
+    """Prefill and decode of Fekulix beside Qwen3 at equal width, depth, feed-forward and vocabulary."""
+    import torch
+
+    from miniserve_b200.config import preset
+    from miniserve_b200.engine import LLM
+    from miniserve_b200.engine.step import StepRow
+
+    peaks = load_peaks()
+    out = {"impl": "ours", "config": "fekulix", "dtype": "bf16", "data": "synthetic (random-init weights, uniform token ids)",
+           "batch": args.batch, "context": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "peaks": peaks["source"], "sizes": {}}
+    steps = min(args.steps, 64)
+    for size in ("0.6b", "1.7b"):
+        q = preset(size)
+        if args.layers is not None:
+            q["num_hidden_layers"] = args.layers
+        f = fekulix_config(q["hidden_size"], q["intermediate_size"], q["num_hidden_layers"], q["vocab_size"],
+                           q["num_attention_heads"], q["num_key_value_heads"])
+        entry = {}
+        for name, raw in (("fekulix", f), ("qwen3", q)):
+            llm = LLM(random=raw, weights_seed=0, dtype="bfloat16", kv_pool_tokens=10 * (CONTEXT + steps + 64) + 4096, page_size=16,
+                      max_running=16, chunked_prefill_size=2048, cuda_graph=not args.no_graph)
+            eng = llm.engine
+            ms, launches, mean_ctx = time_decode(eng, args.batch, CONTEXT, steps, args.warmup)
+            pre_ms = time_prefill(eng, PREFILL_TOKENS)
+            step_bytes = llm.model.weight_bytes() + args.batch * (mean_ctx * eng.cache.bytes_per_token() + 2 * eng.cache.state_bytes() / (eng.cache.max_requests + 1))
+            res = {"decode_tok_s": round(args.batch * 1000.0 / ms, 1), "decode_ms": round(ms, 4), "decode_launches": round(launches, 1),
+                   "decode_hbm_frac": round(step_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                   "prefill_tok_s": round(PREFILL_TOKENS * 1000.0 / pre_ms, 1), "prefill_ms": round(pre_ms, 4),
+                   "weight_bytes": llm.model.weight_bytes()}
+            if args.kernels:
+                rng = random.Random(3)
+                ids = [rng.randrange(q["vocab_size"]) for _ in range(PREFILL_TOKENS)]
+
+                def prefill_once():
+                    rc = eng.cache.new_request()
+                    eng.step_fn.run([StepRow(rc, ids, (PREFILL_TOKENS - 1,))])
+                    eng.cache.release(rc)
+
+                res["prefill_kernels"] = kernel_times(prefill_once)
+                bench = DecodeBench(eng, args.batch, CONTEXT)
+                for _ in range(3):
+                    bench.step_device()
+                res["decode_kernels"] = kernel_times(bench.step_device, repeats=8)
+                bench.release()
+            entry[name] = res
+            del llm, eng
+            torch.cuda.empty_cache()
+        entry["decode_ratio"] = round(entry["fekulix"]["decode_tok_s"] / entry["qwen3"]["decode_tok_s"], 3)
+        entry["prefill_ratio"] = round(entry["fekulix"]["prefill_tok_s"] / entry["qwen3"]["prefill_tok_s"], 3)
+        out["sizes"][size] = entry
+    return out
+
+
 WORKLOADS = {
     # the reference's serving workload at Qwen3-8B sizes: continuous batching with a 2,048-token chunk budget, prompts uniform in [128, 4096]
     "8b": dict(preset="8b", requests=32, prompt=(128, 4096), new_tokens=128, pool_pages=None),
@@ -503,8 +604,10 @@ def main() -> int:
     ap.add_argument("--no-graph", action="store_true", help="run decode steps without CUDA graphs")
     ap.add_argument("--profile-range", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
-    ap.add_argument("--config", choices=["0.6b", "8b", "32b"], default="0.6b",
-                    help="0.6b: the benchmark line; 8b, 32b: the larger workloads through Engine.generate (a line of their own)")
+    ap.add_argument("--config", choices=["0.6b", "8b", "32b", "fekulix"], default="0.6b",
+                    help="0.6b: the benchmark line; 8b, 32b: the larger workloads through Engine.generate (a line of their own); "
+                         "fekulix: prefill and decode of the Fekulix design beside Qwen3 at equal sizes (a line of its own)")
+    ap.add_argument("--kernels", action="store_true", help="with --config fekulix: also device time per kernel of a prompt step and a decode step")
     ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                     help="measure only the decode steps or only the prefill (for profiling); the line then lacks the other parts")
     args = ap.parse_args()
@@ -517,7 +620,9 @@ def main() -> int:
         args.warmup = 3
     global PROFILE_RANGE
     PROFILE_RANGE = args.profile_range
-    if args.config != "0.6b" and args.impl == "ours":
+    if args.config == "fekulix" and args.impl == "ours":
+        result = run_fekulix(args)
+    elif args.config != "0.6b" and args.impl == "ours":
         result = run_workload(args)
     else:
         result = run_reference(args) if args.impl == "reference" else run_ours(args)

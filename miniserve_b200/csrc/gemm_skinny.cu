@@ -29,7 +29,7 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   return v;
 }
 
-// MODE 0: bf16 out [M, N]; 1: float32 out [M, N];
+// MODE 0: bf16 out [M, N]; 1: float32 out [M, N]; 2: bf16 out = gelu_tanh(x W^T);
 // MODE 3: W is a stacked gate|up weight [2N, K] and out [M, N] = silu(x Wg^T) * (x Wu^T) in bf16
 // (miniserve/model/qwen3.py:128-131): the CTA takes 8 gate rows as the lower half of its fragments
 // and the 8 up rows that belong to them as the upper half, so both factors of an output meet in it.
@@ -149,6 +149,11 @@ gemm_skinny_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ X, 
     const size_t o = (size_t)tok * N + n0 + row;
     if (MODE == 0) {
       reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(s);
+    } else if (MODE == 2) {
+      // the tanh form of GELU on the product rounded to bfloat16, as when it is stored in between
+      const float z = __bfloat162float(__float2bfloat16_rn(s));
+      reinterpret_cast<__nv_bfloat16*>(out)[o] =
+          __float2bfloat16_rn(0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))));
     } else {
       reinterpret_cast<float*>(out)[o] = s;
     }
@@ -355,6 +360,14 @@ MS_EXPORT int ms_gemm_skinny_bf16(void* out, const void* X, const void* W, int M
   }
   if (out_mode == 0) return wide ? launch_skinny<2, 0>(out, X, W, M, N, K, stream) : launch_skinny<1, 0>(out, X, W, M, N, K, stream);
   return wide ? launch_skinny<2, 1>(out, X, W, M, N, K, stream) : launch_skinny<1, 1>(out, X, W, M, N, K, stream);
+}
+
+// out [M, N] bfloat16 = gelu_tanh(X W^T), the activation in the product's epilogue.
+MS_EXPORT int ms_gemm_skinny_gelu_bf16(void* out, const void* X, const void* W, int M, int N, int K, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  if (int rc = check_skinny(W, M, N, K, 0)) return rc;
+  MS_CHECK_ARG((uintptr_t)X % 16 == 0, "gemm_skinny: the activations must be 16-byte aligned");
+  return M > 8 ? launch_skinny<2, 2>(out, X, W, M, N, K, stream) : launch_skinny<1, 2>(out, X, W, M, N, K, stream);
 }
 
 // out [M, N] bfloat16 = silu(X Wg^T) * (X Wu^T) for the stacked weight W = [Wg; Wu] of 2N rows.

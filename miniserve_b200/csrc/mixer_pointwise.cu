@@ -48,6 +48,17 @@ __global__ void gelu_tanh_kernel(T* __restrict__ out, const T* __restrict__ x, l
   Elem<T>::store(out + i, 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))));
 }
 
+__global__ void gelu_tanh_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x, long long n8) {
+  pdl_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  float v[8];
+  bf16x8_to_float(reinterpret_cast<const uint4*>(x)[i], v);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) v[e] = 0.5f * v[e] * (1.0f + tanhf(0.7978845608028654f * (v[e] + 0.044715f * v[e] * v[e] * v[e])));
+  reinterpret_cast<uint4*>(out)[i] = float_to_bf16x8(v);
+}
+
 __global__ void scale_f32_kernel(float* __restrict__ x, float s, long long n) {
   pdl_prologue();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -183,6 +194,9 @@ MS_EXPORT int ms_gelu_tanh(void* out, const void* x, long long n, int dtype, cud
   const unsigned blocks = (unsigned)((n + 255) / 256);
   if (dtype == MS_F32)
     MS_LAUNCH(gelu_tanh_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)x, n);
+  else if (n % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)x % 16 == 0)
+    MS_LAUNCH(gelu_tanh_bf16x8_kernel, (unsigned)((n / 8 + 255) / 256), 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)x,
+              n / 8);
   else
     MS_LAUNCH(gelu_tanh_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, n);
   return 0;

@@ -10,8 +10,10 @@
 // The columns of S never meet: column j of S and element j of v, u and o make a recurrence of their
 // own. So a CTA takes (request, head, a run of columns), a column is held by L threads of a warp
 // (16 key channels each, in registers), and the sums over key channels go through that lane group in a
-// fixed order. Tokens are taken in chunks: the CTA stages the chunk's q, k, v (and beta) and works out
-// the decays in float32, all threads at once, then walks the chunk token by token. A request's result
+// fixed order. Tokens are taken in chunks: the CTA stages the chunk's q, k, v, decays (and beta) in
+// float32, all threads at once, then walks the chunk token by token. The decays of a prompt portion are
+// worked out beforehand by a kernel of their own (exponentials and logarithms for every token and
+// channel at once, instead of inside the serial walk); a decode step works them out while staging. A request's result
 // is the same bit for bit however its tokens are cut into steps and whatever else the step holds: the
 // state is carried in float32 and nothing in a token's arithmetic depends on the chunking.
 //
@@ -22,35 +24,72 @@
 
 namespace ms {
 
-constexpr int SCAN_KPT = 16;      // key channels per thread
-constexpr int SCAN_THREADS = 256;
+constexpr int SCAN_MAX_KPT = 16;  // key channels per thread: 16, 8 or 4 (fewer channels a thread, more threads a column)
+constexpr int SCAN_THREADS = 256;  // at most; a launch with few (request, head) pairs takes fewer columns per CTA and more CTAs
+
+inline int scan_sm_count() {
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      sm_count = 0;
+  }
+  return sm_count;
+}
 
 __device__ __forceinline__ float softplusf(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+__device__ __forceinline__ float decay_of(float z, float coef, float sign) { return expf(-coef * softplusf(sign * z)); }
 
-template <typename TIn, typename TZ, bool DELTA>
+// decay[t, h * dk + i] = exp(-c_h softplus(sign (z[t, h * dk + i] + bias[h * dk + i]))) for every token of a step,
+// and (with beta) sigmoid(beta[t, h]) behind a row's decays: out [T, H * dk (+ H)] float32.
+template <typename TZ>
+__global__ void decay_from_logits_kernel(float* __restrict__ out, const TZ* __restrict__ z, int ld_z, const float* __restrict__ z_bias,
+                                         const float* __restrict__ decay_coef, float z_sign, const TZ* __restrict__ beta,
+                                         int ld_beta, long long items, int H, int dk) {
+  pdl_prologue();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= items) return;
+  const int width = H * dk + (beta ? H : 0);
+  const long long t = idx / width;
+  const int c = (int)(idx - t * width);
+  if (c < H * dk) out[idx] = decay_of(Elem<TZ>::load(z + t * ld_z + c) + z_bias[c], decay_coef[c / dk], z_sign);
+  else out[idx] = 1.0f / (1.0f + expf(-Elem<TZ>::load(beta + t * ld_beta + (c - H * dk))));
+}
+
+// eight consecutive elements as float32 (a 16-byte aligned address)
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) { bf16x8_to_float(*reinterpret_cast<const uint4*>(p), f); }
+__device__ __forceinline__ void load8(const float* p, float (&f)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+template <typename TIn, typename TZ, bool DELTA, int SCAN_KPT>
 __global__ void __launch_bounds__(SCAN_THREADS)
 decay_scan_kernel(float* __restrict__ o_out,   // [T, H, dv]
                   float* __restrict__ state,   // [slots, H, dv, dk]
                   const TIn* __restrict__ q, int ld_q, const TIn* __restrict__ k, int ld_k, int qk_group,
                   const TIn* __restrict__ v, int ld_v,
                   const TZ* __restrict__ z, int ld_z, const float* __restrict__ z_bias, const float* __restrict__ decay_coef,
-                  float z_sign, const TZ* __restrict__ beta, int ld_beta,
+                  float z_sign, int z_is_decay, const TZ* __restrict__ beta, int ld_beta,
                   const int* __restrict__ cu_q, const int* __restrict__ q_start, const int* __restrict__ state_slot,
-                  int H, int dk, int dv, int L, int chunk, float q_scale) {
-  extern __shared__ float smem[];
+                  int H, int dk, int dv, int L, int chunk, float q_scale, int vec) {
+  // words a thread's channels take in shared memory: padded so that the 16-byte loads of a quarter warp's lanes fall on different banks
+  constexpr int SCAN_SEG = SCAN_KPT == 4 ? 4 : SCAN_KPT + 4;
+  extern __shared__ __align__(16) float smem[];
   pdl_prologue();
   const int r = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-  const int cols = SCAN_THREADS / L;
+  const int threads = blockDim.x;
+  const int cols = threads / L;
   const int col = tid / L, l = tid - col * L;
   const int j = blockIdx.z * cols + col;
   const bool active = j < dv;
-  const int dkp = L * (SCAN_KPT + 1);  // a lane's 16 channels, then one word of padding: lanes fall on different banks
+  const int dkp = L * SCAN_SEG;
   float* qs = smem;
   float* ks = qs + (size_t)chunk * dkp;
   float* ds = ks + (size_t)chunk * dkp;
   float* vs = ds + (size_t)chunk * dkp;   // [chunk, cols]
   float* bs = vs + (size_t)chunk * cols;  // [chunk]
-  for (int i = tid; i < 3 * chunk * dkp; i += SCAN_THREADS) smem[i] = 0.f;  // channels beyond dk stay zero
+  for (int i = tid; i < 3 * chunk * dkp; i += threads) smem[i] = 0.f;  // channels beyond dk stay zero
 
   const int t0 = cu_q[r], t1 = cu_q[r + 1];
   const int slot = state_slot[r];
@@ -68,29 +107,65 @@ decay_scan_kernel(float* __restrict__ o_out,   // [T, H, dv]
 
   for (int c0 = t0; c0 < t1; c0 += chunk) {
     const int n = min(chunk, t1 - c0);
-    for (int idx = tid; idx < n * dk; idx += SCAN_THREADS) {
+    if (vec) {
+      // eight channels per trip, 16-byte loads; the trips are unrolled so that a thread's loads are in flight together
+      const int groups = dk >> 3;
+#pragma unroll 4
+      for (int idx = tid; idx < n * groups; idx += threads) {
+        const int tt = idx / groups, i = (idx - tt * groups) << 3;
+        const size_t tok = (size_t)(c0 + tt);
+        float fq[8], fk[8], fz[8];
+        load8(q + tok * ld_q + (size_t)qk_head * dk + i, fq);
+        load8(k + tok * ld_k + (size_t)qk_head * dk + i, fk);
+        load8(z + tok * ld_z + (size_t)h * dk + i, fz);
+        const int at = tt * dkp + (i / SCAN_KPT) * SCAN_SEG + (i % SCAN_KPT);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          fq[e] *= q_scale;
+          if (!z_is_decay) fz[e] = decay_of(fz[e] + z_bias[(size_t)h * dk + i + e], coef, z_sign);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; e += 4) {
+          *reinterpret_cast<float4*>(qs + at + e) = make_float4(fq[e], fq[e + 1], fq[e + 2], fq[e + 3]);
+          *reinterpret_cast<float4*>(ks + at + e) = make_float4(fk[e], fk[e + 1], fk[e + 2], fk[e + 3]);
+          *reinterpret_cast<float4*>(ds + at + e) = make_float4(fz[e], fz[e + 1], fz[e + 2], fz[e + 3]);
+        }
+      }
+    } else
+    for (int idx = tid; idx < n * dk; idx += threads) {
       const int tt = idx / dk, i = idx - tt * dk;
       const size_t tok = (size_t)(c0 + tt);
-      const int at = tt * dkp + i + i / SCAN_KPT;
+      const int at = tt * dkp + (i / SCAN_KPT) * SCAN_SEG + (i % SCAN_KPT);
       qs[at] = Elem<TIn>::load(q + tok * ld_q + (size_t)qk_head * dk + i) * q_scale;
       ks[at] = Elem<TIn>::load(k + tok * ld_k + (size_t)qk_head * dk + i);
-      const float zz = Elem<TZ>::load(z + tok * ld_z + (size_t)h * dk + i) + z_bias[(size_t)h * dk + i];
-      ds[at] = expf(-coef * softplusf(z_sign * zz));
+      const float zz = Elem<TZ>::load(z + tok * ld_z + (size_t)h * dk + i);
+      ds[at] = z_is_decay ? zz : decay_of(zz + z_bias[(size_t)h * dk + i], coef, z_sign);
     }
-    for (int idx = tid; idx < n * cols; idx += SCAN_THREADS) {
+#pragma unroll 8
+    for (int idx = tid; idx < n * cols; idx += threads) {
       const int tt = idx / cols, c = idx - tt * cols;
       const int jj = blockIdx.z * cols + c;
       vs[idx] = jj < dv ? Elem<TIn>::load(v + (size_t)(c0 + tt) * ld_v + (size_t)h * dv + jj) : 0.f;
     }
     if (DELTA) {
-      for (int tt = tid; tt < n; tt += SCAN_THREADS)
-        bs[tt] = 1.0f / (1.0f + expf(-Elem<TZ>::load(beta + (size_t)(c0 + tt) * ld_beta + h)));
+      for (int tt = tid; tt < n; tt += threads)
+        {
+          const float b = Elem<TZ>::load(beta + (size_t)(c0 + tt) * ld_beta + h);
+          bs[tt] = z_is_decay ? b : 1.0f / (1.0f + expf(-b));
+        }
     }
     __syncthreads();
+    // (two tokens a trip: the lane group's exchange for one token's read-out overlaps the next token's products)
+#pragma unroll 2
     for (int tt = 0; tt < n; ++tt) {
-      const float* qt = qs + tt * dkp + l * (SCAN_KPT + 1);
-      const float* kt = ks + tt * dkp + l * (SCAN_KPT + 1);
-      const float* dt = ds + tt * dkp + l * (SCAN_KPT + 1);
+      float qt[SCAN_KPT], kt[SCAN_KPT], dt[SCAN_KPT];
+#pragma unroll
+      for (int e = 0; e < SCAN_KPT; e += 4) {
+        const int at = tt * dkp + l * SCAN_SEG + e;
+        *reinterpret_cast<float4*>(qt + e) = *reinterpret_cast<const float4*>(qs + at);
+        *reinterpret_cast<float4*>(kt + e) = *reinterpret_cast<const float4*>(ks + at);
+        *reinterpret_cast<float4*>(dt + e) = *reinterpret_cast<const float4*>(ds + at);
+      }
       const float vj = vs[tt * cols + col];
       // sums over a thread's channels in four interleaved chains (a fixed order), so that the token's
       // critical path is four products deep and not sixteen
@@ -227,44 +302,70 @@ __global__ void head_norm_gate_kernel(T* __restrict__ out, int ld_out, const flo
   }
 }
 
-template <typename TIn, typename TZ, bool DELTA>
-int launch_scan(float* o_out, float* state, const void* q, int ld_q, const void* k, int ld_k, int qk_group, const void* v, int ld_v,
-                const void* z, int ld_z, const float* z_bias, const float* decay_coef, float z_sign, const void* beta, int ld_beta,
-                const int* cu_q, const int* q_start, const int* state_slot, int num_rows, int H, int dk, int dv, float q_scale,
+template <typename TIn, typename TZ, bool DELTA, int SCAN_KPT>
+int launch_scan_kpt(float* o_out, float* state, const void* q, int ld_q, const void* k, int ld_k, int qk_group, const void* v, int ld_v,
+                const void* z, int ld_z, const float* z_bias, const float* decay_coef, float z_sign, int z_is_decay, const void* beta,
+                int ld_beta, const int* cu_q, const int* q_start, const int* state_slot, int num_rows, int H, int dk, int dv, float q_scale,
                 cudaStream_t stream) {
+  constexpr int SCAN_SEG = SCAN_KPT == 4 ? 4 : SCAN_KPT + 4;
   int L = 1;
   while (L * SCAN_KPT < dk) L <<= 1;
-  const int cols = SCAN_THREADS / L;
-  const int dkp = L * (SCAN_KPT + 1);
+  // Columns are independent, and a token's work is one short dependent chain per warp: a launch is
+  // as fast as its CTAs are many. Halve the CTA (down to one warp) until there are two CTAs per SM.
+  const int sm_count = scan_sm_count();
+  MS_CHECK_ARG(sm_count > 0 && L <= 32, "decay_scan: no device, or a key size of %d for %d channels a thread", dk, SCAN_KPT);
+  int threads = SCAN_THREADS;
+  while (threads > 32 && (long long)num_rows * H * ((dv + threads / L - 1) / (threads / L)) < 2LL * sm_count) threads >>= 1;
+  const int cols = threads / L;
+  const int dkp = L * SCAN_SEG;
   const int per_token = (3 * dkp + cols + 1) * (int)sizeof(float);
   int chunk = (40 * 1024) / per_token;
   chunk = chunk > 32 ? 32 : (chunk < 1 ? 1 : chunk);
   const size_t smem = (size_t)chunk * per_token;
-  auto kernel = decay_scan_kernel<TIn, TZ, DELTA>;
+  auto kernel = decay_scan_kernel<TIn, TZ, DELTA, SCAN_KPT>;
   const dim3 grid(num_rows, H, (dv + cols - 1) / cols);
-  MS_LAUNCH(kernel, grid, SCAN_THREADS, smem, stream, o_out, state, (const TIn*)q, ld_q, (const TIn*)k, ld_k, qk_group,
-            (const TIn*)v, ld_v, (const TZ*)z, ld_z, z_bias, decay_coef, z_sign, (const TZ*)beta, ld_beta, cu_q, q_start, state_slot,
-            H, dk, dv, L, chunk, q_scale);
+  // 16-byte loads while staging: every row of q, k and z starts on 16 bytes and heads are whole groups of eight
+  const int in8 = 16 / (int)sizeof(TIn), z8 = 16 / (int)sizeof(TZ);
+  const int vec = dk % 8 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)k % 16 == 0 && (uintptr_t)z % 16 == 0 && ld_q % in8 == 0 &&
+                  ld_k % in8 == 0 && ld_z % z8 == 0;
+  MS_LAUNCH(kernel, grid, threads, smem, stream, o_out, state, (const TIn*)q, ld_q, (const TIn*)k, ld_k, qk_group,
+            (const TIn*)v, ld_v, (const TZ*)z, ld_z, z_bias, decay_coef, z_sign, z_is_decay, (const TZ*)beta, ld_beta, cu_q, q_start, state_slot,
+            H, dk, dv, L, chunk, q_scale, vec);
   return 0;
+}
+
+// A token's work in a warp is one dependent chain, so a launch is as fast as its warps are many: with few
+// (request, head) pairs a column is spread over more threads (4 or 8 channels each instead of 16), at the
+// price of a longer exchange within the lane group. The sums' order follows the channels a thread holds,
+// so the choice must not depend on the batch: it follows the heads' sizes alone.
+template <typename TIn, typename TZ, bool DELTA, typename... Args>
+int launch_scan(int H, int dk, int dv, Args... args) {
+  const long long threads16 = (long long)H * dv * ((dk + 15) / 16);  // of one request, at 16 channels a thread
+  const int sm_count = scan_sm_count();
+  if (dk <= 32 * 4 && threads16 * 4 <= 128LL * sm_count) return launch_scan_kpt<TIn, TZ, DELTA, 4>(args...);
+  if (dk <= 32 * 8 && threads16 * 2 <= 128LL * sm_count) return launch_scan_kpt<TIn, TZ, DELTA, 8>(args...);
+  return launch_scan_kpt<TIn, TZ, DELTA, 16>(args...);
 }
 
 }  // namespace ms
 
 using namespace ms;
 
-// in_dtype: of q, k, v; z_dtype: of z and beta. delta: 0 decay rule, 1 delta rule.
+// in_dtype: of q, k, v; z_dtype: of z and beta. delta: 0 decay rule, 1 delta rule. z_is_decay: z and beta are
+// float32 and hold the decays and sigmoid(beta) themselves (ms_decay_from_logits), not their logits.
 MS_EXPORT int ms_decay_scan(float* o_out, float* state, const void* q, int ld_q, const void* k, int ld_k, int qk_group,
                             const void* v, int ld_v, const void* z, int ld_z, const float* z_bias, const float* decay_coef,
-                            float z_sign, const void* beta, int ld_beta, const int* cu_q, const int* q_start,
+                            float z_sign, int z_is_decay, const void* beta, int ld_beta, const int* cu_q, const int* q_start,
                             const int* state_slot, int num_rows, int H, int dk, int dv, float q_scale, int delta, int in_dtype,
                             int z_dtype, cudaStream_t stream) {
   if (num_rows == 0) return 0;
-  MS_CHECK_ARG(H > 0 && dk > 0 && dv > 0 && dk <= 32 * SCAN_KPT, "decay_scan: key size %d is outside 1..%d", dk, 32 * SCAN_KPT);
+  MS_CHECK_ARG(H > 0 && dk > 0 && dv > 0 && dk <= 32 * SCAN_MAX_KPT, "decay_scan: key size %d is outside 1..%d", dk, 32 * SCAN_MAX_KPT);
   MS_CHECK_ARG(qk_group > 0 && H % qk_group == 0, "decay_scan: %d heads are not a multiple of the group of %d", H, qk_group);
   MS_CHECK_ARG(!delta || beta != nullptr, "decay_scan: the delta rule needs beta");
+  MS_CHECK_ARG(!z_is_decay || z_dtype == MS_F32, "decay_scan: decays worked out beforehand are float32");
 #define MS_SCAN(TIN, TZZ, D)                                                                                                  \
-  return launch_scan<TIN, TZZ, D>(o_out, state, q, ld_q, k, ld_k, qk_group, v, ld_v, z, ld_z, z_bias, decay_coef, z_sign, beta, \
-                                  ld_beta, cu_q, q_start, state_slot, num_rows, H, dk, dv, q_scale, stream)
+  return launch_scan<TIN, TZZ, D>(H, dk, dv, o_out, state, q, ld_q, k, ld_k, qk_group, v, ld_v, z, ld_z, z_bias, decay_coef, z_sign, z_is_decay, \
+                                  beta, ld_beta, cu_q, q_start, state_slot, num_rows, H, dk, dv, q_scale, stream)
   if (in_dtype == MS_F32 && z_dtype == MS_F32) {
     if (delta) MS_SCAN(float, float, true);
     MS_SCAN(float, float, false);
@@ -273,12 +374,30 @@ MS_EXPORT int ms_decay_scan(float* o_out, float* state, const void* q, int ld_q,
     if (delta) MS_SCAN(float, __nv_bfloat16, true);
     MS_SCAN(float, __nv_bfloat16, false);
   }
+  if (in_dtype == MS_BF16 && z_dtype == MS_F32) {
+    if (delta) MS_SCAN(__nv_bfloat16, float, true);
+    MS_SCAN(__nv_bfloat16, float, false);
+  }
   if (in_dtype == MS_BF16 && z_dtype == MS_BF16) {
     if (delta) MS_SCAN(__nv_bfloat16, __nv_bfloat16, true);
     MS_SCAN(__nv_bfloat16, __nv_bfloat16, false);
   }
 #undef MS_SCAN
   return ms::fail("decay_scan: unsupported dtypes (%d, %d)", in_dtype, z_dtype);
+}
+
+MS_EXPORT int ms_decay_from_logits(float* out, const void* z, int ld_z, const float* z_bias, const float* decay_coef, float z_sign,
+                                   const void* beta, int ld_beta, int num_tokens, int H, int dk, int dtype, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  const long long items = (long long)num_tokens * (H * dk + (beta ? H : 0));
+  const unsigned blocks = (unsigned)((items + 255) / 256);
+  if (dtype == MS_F32)
+    MS_LAUNCH(decay_from_logits_kernel<float>, blocks, 256, 0, stream, out, (const float*)z, ld_z, z_bias, decay_coef, z_sign,
+              (const float*)beta, ld_beta, items, H, dk);
+  else
+    MS_LAUNCH(decay_from_logits_kernel<__nv_bfloat16>, blocks, 256, 0, stream, out, (const __nv_bfloat16*)z, ld_z, z_bias, decay_coef,
+              z_sign, (const __nv_bfloat16*)beta, ld_beta, items, H, dk);
+  return 0;
 }
 
 MS_EXPORT int ms_conv_silu_unit(float* out, const void* proj, int ld, const void* conv_state, const float* w,

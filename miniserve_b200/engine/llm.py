@@ -33,7 +33,7 @@ class LLM:
             self.raw_config, self.config, self.model = load_model(model, dtype, device)
         else:
             raw = preset(random) if isinstance(random, str) else dict(random)
-            big = raw.get("hidden_size", 0) * raw.get("num_hidden_layers", 0) > 4096
+            big = (raw.get("hidden_size") or raw.get("width", 0)) * (raw.get("num_hidden_layers") or len(raw.get("layers", ()))) > 4096
             self.raw_config, self.config, self.model = random_model(raw, weights_seed, dtype, device,
                                                                     draw_on_device=big)
         self.engine = Engine(self.model, **engine_kwargs)

@@ -297,6 +297,23 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = Non
     return out
 
 
+def linear_gelu_tanh(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, stream=None) -> torch.Tensor:
+    """out [M, N] = gelu_tanh(x W^T). bfloat16 with at most 16 rows where the weight-streaming kernel is
+    the choice for the plain product: one kernel with the activation in its epilogue (the product is
+    rounded to bfloat16 first, as when it is stored in between). Otherwise the product, then the
+    activation kernel in place."""
+    if x.dtype == torch.bfloat16 and not _tc_decode_ok(x, weight, out) and _skinny_ok(x, weight):
+        _check_dev(x, weight, out)
+        m, kdim = x.shape
+        assert weight.shape[1] == kdim and out.shape == (m, weight.shape[0]) and out.dtype == torch.bfloat16
+        native.kernel_check(native.kernels().ms_gemm_skinny_gelu_bf16(_ptr(out), _ptr(x), _ptr(weight), m, weight.shape[0], kdim,
+                                                                      _stream(stream)))
+        return out
+    linear(x, weight, out=out, stream=stream)
+    gelu_tanh(out, out, stream=stream)
+    return out
+
+
 def silu_mul_is_fused(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bool:
     """Whether ``linear_silu_mul`` runs as one kernel for these operands (then it needs no scratch)."""
     if x.dtype != torch.bfloat16:

@@ -115,9 +115,19 @@ def decay_scan(o_out, state, q, k, v, z, z_bias, decay_coef, z_sign: float, beta
     groups = q.shape[1] // dk
     assert q.shape == (t, groups * dk) and k.shape == q.shape and v.shape == (t, heads * dv) and z.shape == (t, heads * dk)
     assert q.dtype == k.dtype == v.dtype and (beta is None or beta.dtype == z.dtype)
+    ready = 0
+    if not ctx.decode_only:
+        # a prompt portion: exponentials and logarithms for all tokens at once, not inside the serial walk
+        # (a decode step, one token a row, works them out while it stages the token)
+        width = heads * dk + (heads if beta is not None else 0)
+        pre = ctx.buffer("scan.decay", (t, width), torch.float32, o_out.device)
+        native.kernel_check(native.kernels().ms_decay_from_logits(
+            _ptr(pre), _ptr(z), _rows(z), _ptr(z_bias), _ptr(decay_coef), float(z_sign), _ptr(beta),
+            0 if beta is None else _rows(beta), t, heads, dk, _dt(z.dtype), ctx.stream))
+        z, beta, ready = pre[:, :heads * dk], (pre[:, heads * dk:] if beta is not None else None), 1
     native.kernel_check(native.kernels().ms_decay_scan(
         _ptr(o_out), _ptr(state), _ptr(q), _rows(q), _ptr(k), _rows(k), heads // groups, _ptr(v), _rows(v), _ptr(z), _rows(z),
-        _ptr(z_bias), _ptr(decay_coef), float(z_sign), _ptr(beta), 0 if beta is None else _rows(beta), _ptr(ctx.cu_q),
+        _ptr(z_bias), _ptr(decay_coef), float(z_sign), ready, _ptr(beta), 0 if beta is None else _rows(beta), _ptr(ctx.cu_q),
         _ptr(ctx.q_start), _ptr(ctx.state_slot), ctx.num_rows, heads, dk, dv, float(q_scale), int(delta), _dt(q.dtype),
         _dt(z.dtype), ctx.stream))
 

@@ -99,6 +99,7 @@ def kernels():
     _declare(lib, "ms_add_rmsnorm", [_p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _p])
     _declare(lib, "ms_gemm_skinny_gate_up_bf16", [_p, _p, _p, _i, _i, _i, _p])
     _declare(lib, "ms_gemm_skinny_bf16", [_p, _p, _p, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_gemm_skinny_gelu_bf16", [_p, _p, _p, _i, _i, _i, _p])
     _declare(lib, "ms_gemm_skinny_set_stream", [_i], None)
     _declare(lib, "ms_silu_mul", [_p, _p, _i, _i, _i, _p])
     _declare(lib, "ms_to_float", [_p, _p, _ll, _i, _p])
@@ -115,8 +116,9 @@ def kernels():
     _declare(lib, "ms_axpby", [_p, _p, _p, _f, _f, _ll, _i, _p])
     _declare(lib, "ms_head_gate", [_p, _i, _p, _p, _i, _i, _i, _i, _i, _f, _i, _p])
     _declare(lib, "ms_qkv_prepare", [_p] * 4 + [_i] * 4 + [_p] * 7 + [_i] * 8 + [_f, _i, _i, _p, _i, _p])
-    _declare(lib, "ms_decay_scan", [_p, _p, _p, _i, _p, _i, _i, _p, _i, _p, _i, _p, _p, _f, _p, _i, _p, _p, _p,
+    _declare(lib, "ms_decay_scan", [_p, _p, _p, _i, _p, _i, _i, _p, _i, _p, _i, _p, _p, _f, _i, _p, _i, _p, _p, _p,
                                     _i, _i, _i, _i, _f, _i, _i, _i, _p])
+    _declare(lib, "ms_decay_from_logits", [_p, _p, _i, _p, _p, _f, _p, _i, _i, _i, _i, _i, _p])
     _declare(lib, "ms_conv_silu_unit", [_p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p])
     _declare(lib, "ms_conv_state_update", [_p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p])
     _declare(lib, "ms_head_norm_gate", [_p, _i, _p, _p, _p, _i, _i, _i, _i, _f, _f, _i, _i, _p])

@@ -74,6 +74,6 @@ class DenseMLP(Part):
 
     def forward(self, x, ctx) -> torch.Tensor:
         t, dt, dev = x.shape[0], self.env.dtype, self.w_down.device
-        act = ops.linear(x, self.w_up, stream=ctx.stream, out=ctx.buffer("mlp.act", (t, self.inter), dt, dev))
-        ops.gelu_tanh(act, act, stream=ctx.stream)
+        # the activation in the product's epilogue where there is such a kernel (decode steps)
+        act = ops.linear_gelu_tanh(x, self.w_up, ctx.buffer("mlp.act", (t, self.inter), dt, dev), stream=ctx.stream)
         return ops.linear(act, self.w_down, stream=ctx.stream, out=ctx.buffer("mlp.down", (t, self.hidden), dt, dev))
