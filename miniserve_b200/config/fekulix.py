@@ -50,9 +50,12 @@ class FekulixConfig:
                 raise NotImplementedError(f"layer {i}: feed-forward kind {mlp.get('kind')!r} is not supported")
             of = entry.get("weights_of")
             if of is not None:
-                of = int(of)
-                if not 0 <= of < len(raw["layers"]) or of == i or raw["layers"][of].get("weights_of") is not None:
-                    raise ValueError(f"layer {i}: weights_of={of} must name another layer that has tensors of its own")
+                of, seen = int(of), {i}
+                while 0 <= of < len(raw["layers"]) and of not in seen and raw["layers"][of].get("weights_of") is not None:
+                    seen.add(of)  # a layer that borrows from a borrower runs with the tensors at the end of the chain
+                    of = int(raw["layers"][of]["weights_of"])
+                if not 0 <= of < len(raw["layers"]) or of in seen:
+                    raise ValueError(f"layer {i}: weights_of={entry.get('weights_of')} must lead to another layer that has tensors of its own")
                 if raw["layers"][of].get("type") != kind:
                     raise ValueError(f"layer {i} ({kind}) cannot run with the weights of layer {of} ({raw['layers'][of].get('type')})")
             layers.append(FekulixLayer(kind, entry["mixer"], int(mlp["ff"]) if mlp is not None else None, of))
@@ -87,8 +90,9 @@ def complete_from_shapes(raw: Mapping[str, Any], shapes: Mapping[str, tuple]) ->
     """The ranks of the low-rank projections, read off the checkpoint's tensor shapes."""
     raw = copy.deepcopy(dict(raw))
     for i, entry in enumerate(raw.get("layers", [])):
-        src = entry.get("weights_of", i)
-        src = i if src is None else src
+        src, hops = i, 0
+        while raw["layers"][src].get("weights_of") is not None and hops <= len(raw["layers"]):
+            src, hops = int(raw["layers"][src]["weights_of"]), hops + 1
         m = entry.get("mixer", {})
         if entry.get("type") == "parallel":
             name = f"l{src}.mix.right.a1"

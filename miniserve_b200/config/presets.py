@@ -18,7 +18,28 @@ def _qwen3(hidden, inter, vocab, layers, heads, kv_heads, head_dim, theta, eps, 
     )
 
 
+def _fekulix(width, vocab, ff, pattern, left, right, delta) -> dict:
+    """A Fekulix config.json: ``pattern`` is a string of P (parallel layer) and D (channel_delta layer); a
+    layer written in lower case runs with the tensors of the first layer of its kind."""
+    first = {"P": pattern.index("P") if "P" in pattern else None, "D": pattern.index("D") if "D" in pattern else None}
+    layers = []
+    for ch in pattern:
+        kind = ch.upper()
+        entry = ({"type": "parallel", "mixer": {"left": dict(left), "left_scale": 1.0, "right": dict(right), "right_scale": 0.5}}
+                 if kind == "P" else {"type": "channel_delta", "mixer": dict(delta)})
+        entry["mlp"] = {"kind": "dense", "ff": ff}
+        if ch.islower():
+            entry["weights_of"] = first[kind]
+        layers.append(entry)
+    return dict(architecture="Fekulix", width=width, vocab=vocab, logit_scale=1.0, norm={"eps": 1e-6}, layers=layers)
+
+
 PRESETS: dict[str, dict] = {
+    "fekulix-tiny": _fekulix(
+        96, 503, 160, "PDpd",
+        left={"dim": 32, "heads": 6, "kv_heads": 2, "rot": {"base": 10000.0, "dims": 16}, "scale": 32 ** -0.5, "vdim": 16},
+        right={"dim": 16, "heads": 3, "tau": 8.0, "vdim": 32, "decay_rank": 8},
+        delta={"conv": 3, "dim": 24, "heads": 4, "kv_heads": 2, "vdim": 24, "decay_rank": 8, "gate_rank": 16}),
     "tiny-a": _qwen3(64, 128, 256, 2, 4, 2, 16, 10000.0, 1e-6, True, 128),
     "tiny-b": _qwen3(96, 224, 503, 3, 6, 1, 32, 1000000.0, 1e-5, False, 256),
     "0.6b": _qwen3(1024, 3072, 151936, 28, 16, 8, 128, 1000000.0, 1e-6, True, 40960),

@@ -5,6 +5,7 @@ summaries under ``profiles/`` were measured and captured with.
     python -m miniserve_b200.tools.kernel_bench attn_prefill --tokens 2048
     python -m miniserve_b200.tools.kernel_bench skinny --m 8 --n 4096 --k 1024
     python -m miniserve_b200.tools.kernel_bench sample --batch 8 --top-p 0.9
+    python -m miniserve_b200.tools.kernel_bench decay_scan --tokens 2048 --heads 8 --key-dim 64 --value-dim 128 [--delta]
 
 Each case rotates over enough copies of its inputs to exceed the L2 cache, captures one pass over
 all copies in a CUDA graph, and reports the time per launch with the bytes or flops it implies.
@@ -86,7 +87,7 @@ def _time(calls, copies, launches):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
-    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "skinny", "add_rmsnorm", "gemm", "gate_up", "sample"])
+    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "skinny", "add_rmsnorm", "gemm", "gate_up", "sample", "decay_scan"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -103,6 +104,9 @@ def main(argv=None) -> int:
     ap.add_argument("--vocab", type=int, default=151936, help="sample: tokens in a row of logits")
     ap.add_argument("--temperature", type=float, default=0.8, help="sample: 0 is greedy")
     ap.add_argument("--top-p", type=float, default=1.0, help="sample: below 1, the nucleus is found first")
+    ap.add_argument("--key-dim", type=int, default=64, help="decay_scan: key channels of a head")
+    ap.add_argument("--value-dim", type=int, default=128, help="decay_scan: value channels of a head")
+    ap.add_argument("--delta", action="store_true", help="decay_scan: the delta rule instead of the decay rule")
     ap.add_argument("--launches", type=int, default=0, help="run this many plain launches and report nothing")
     args = ap.parse_args(argv)
 
@@ -175,7 +179,7 @@ def main(argv=None) -> int:
 
         def calls(i, stream):
             ops.linear(x, ws[i], out=o, stream=stream)
-    else:
+    elif args.kernel == "add_rmsnorm":
         h = args.n
         byts = args.m * h * 10
         work = dict(bytes=byts)
@@ -187,6 +191,31 @@ def main(argv=None) -> int:
 
         def calls(i, stream):
             ops.add_rmsnorm(o, res, delta, w, 1e-6, stream=stream)
+    else:
+        # the linear-attention recurrence: `batch` requests of `tokens` tokens each (1: a decode step), from zero state
+        t, hh, dk, dv, rows = args.tokens * args.batch, args.heads, args.key_dim, args.value_dim, args.batch
+        i32 = dict(dtype=torch.int32, device=dev)
+        bufs = {}
+
+        def buffer(role, shape, dt, device):
+            return bufs.setdefault((role, shape, dt), torch.empty(shape, dtype=dt, device=device))
+
+        ctx = SimpleNamespace(cu_q=torch.arange(0, t + 1, args.tokens, **i32), q_start=torch.zeros(rows, **i32),
+                              state_slot=torch.arange(rows, **i32), num_rows=rows, decode_only=args.tokens == 1, buffer=buffer, stream=0)
+        kind = torch.float32 if args.delta else torch.bfloat16  # the delta rule's q, k, v come from the convolution in float32
+        q, k = (torch.randn(t, hh * dk, device=dev).to(kind) for _ in range(2))
+        v = torch.randn(t, hh * dv, device=dev).to(kind)
+        z = torch.randn(t, hh * dk, device=dev).bfloat16()
+        beta = torch.randn(t, hh, device=dev).bfloat16() if args.delta else None
+        bias, coef = torch.zeros(hh * dk, device=dev), torch.full((hh,), 0.1, device=dev)
+        state, o = torch.zeros(rows + 1, hh, dv, dk, device=dev), torch.empty(t, hh, dv, device=dev)
+        item = 4 if args.delta else 2
+        work = dict(bytes=t * hh * ((2 * dk + dv) * item + dk * 2 + dv * 4) + 2 * rows * hh * dk * dv * 4)
+        copies = 2
+
+        def calls(i, stream):
+            ctx.stream = stream
+            ops.decay_scan(o, state, q, k, v, z, bias, coef, -1.0, beta, ctx, hh, dk, dv, dk ** -0.5, delta=args.delta)
     us = _time(calls, copies, args.launches)
     if us is not None:
         out.update(us_per_launch=round(us, 2), copies=copies)

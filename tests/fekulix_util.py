@@ -58,6 +58,18 @@ def config_b():
     ], width=48, vocab=61, eps=1e-6, logit_scale=0.5)
 
 
+def config_c():
+    """A width and feed-forward sizes that are no multiples of 8, key sizes that are no multiples of 8
+    (the recurrence stages them element by element), five heads, a layer that borrows from a borrower."""
+    return config([
+        delta_layer(heads=5, kv_heads=5, dim=12, vdim=20, conv=4, ff=52, decay_rank=6, gate_rank=10),
+        parallel_layer(heads=5, kv_heads=5, dim=24, vdim=24, rot=6, base=1000.0, scale=0.3, r_heads=3, r_dim=20, r_vdim=12,
+                       tau=2.0, left_scale=0.5, right_scale=2.0, ff=None, decay_rank=4),
+        delta_layer(weights_of=0, heads=5, kv_heads=5, dim=12, vdim=20, conv=4, ff=52, decay_rank=6, gate_rank=10),
+        delta_layer(weights_of=2, heads=5, kv_heads=5, dim=12, vdim=20, conv=4, ff=52, decay_rank=6, gate_rank=10),
+    ], width=36, vocab=53, eps=1e-5, logit_scale=3.0)
+
+
 def tensor_shapes(raw) -> dict[str, tuple]:
     """Names and shapes of a checkpoint of this configuration."""
     w = raw["width"]
@@ -193,3 +205,28 @@ def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
     d = d - d.mean(dim=-1, keepdim=True)
     spread = (want.double() - want.double().mean(dim=-1, keepdim=True)).pow(2).mean().sqrt()
     return (d.pow(2).mean(dim=-1).sqrt().max() / spread).item()
+
+
+class _RoundedProducts(torch.Tensor):
+    """A matrix whose products come back rounded to bfloat16 (and widened again)."""
+
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        args = [a.as_subclass(torch.Tensor) if isinstance(a, _RoundedProducts) else a for a in args]
+        out = func(*args, **(kwargs or {}))
+        name = getattr(func, "__name__", "")
+        if name in ("matmul", "__matmul__", "__rmatmul__"):
+            return out.bfloat16().to(out.dtype)
+        if isinstance(out, torch.Tensor) and name in ("__get__", "t", "transpose"):
+            return out.as_subclass(_RoundedProducts)
+        return out
+
+
+def rounding_noise(folder, ids) -> float:
+    """rel_err of the oracle against itself when every matrix product's result is rounded to bfloat16:
+    what rounding alone costs on this model and these tokens (the engine rounds in more places)."""
+    cfg, w = plain.read_config(folder), plain.read_weights(folder, torch.float64)
+    exact = plain.all_logits(cfg, w, ids)
+    rounded = {k: (v.as_subclass(_RoundedProducts) if v.dim() == 2 and not k.endswith(".conv") and k != "embed" else v)
+               for k, v in w.items()}
+    return rel_err(torch.as_tensor(plain.all_logits(cfg, rounded, ids)).as_subclass(torch.Tensor), exact)

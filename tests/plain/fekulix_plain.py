@@ -194,7 +194,9 @@ def layer_outputs(cfg: dict, weights: dict, ids) -> tuple[torch.Tensor, torch.Te
         return dynamic_tanh(y, weights[name], weights[name + ".b"], weights[name + ".alpha"])
 
     for i, layer in enumerate(cfg["layers"]):
-        src = layer.get("weights_of", i)
+        src = i
+        while cfg["layers"][src].get("weights_of") is not None:  # a layer may run with another layer's tensors
+            src = cfg["layers"][src]["weights_of"]
         pre = f"l{src}."
         w = lambda n, pre=pre: weights[pre + "mix." + n]
         h = norm(pre + "norm1", x)

@@ -34,6 +34,12 @@ def test_config_maps_onto_parts_and_run_order():
     assert decls == fx.tensor_shapes(raw)  # names and shapes as the checkpoint format states them
 
 
+def test_a_borrower_of_a_borrower_runs_with_the_owner_s_tensors():
+    raw = fx.config([fx.parallel_layer(), fx.parallel_layer(weights_of=0), fx.parallel_layer(weights_of=1), fx.delta_layer(ff=40)])
+    _, _, spec = resolve(raw)
+    assert [e.layer for e in spec.run_order] == [0, 0, 0, 1] and len(spec.layers) == 2
+
+
 def test_each_run_entry_has_pages_and_state_of_its_own():
     _, _, spec = resolve(fx.config_a())
     model = DecoderModel(spec, torch.bfloat16, "cpu")
@@ -84,7 +90,8 @@ def test_ranks_come_from_the_checkpoint(tmp_path):
     (lambda r: r["layers"][0].update(type="windowed"), NotImplementedError),
     (lambda r: r["layers"][0]["mlp"].update(kind="experts"), NotImplementedError),
     (lambda r: r["layers"][2].update(weights_of=1), ValueError),   # another kind of layer
-    (lambda r: r["layers"][3].update(weights_of=2), ValueError),   # a layer that has no tensors itself
+    (lambda r: (r["layers"][1].update(weights_of=3), r["layers"][3].update(weights_of=1)), ValueError),   # borrowers in a circle
+    (lambda r: r["layers"][3].update(weights_of=7), ValueError),
     (lambda r: r["layers"][0]["mixer"]["left"].update(kv_heads=3), ValueError),
     (lambda r: r["layers"][0]["mixer"]["left"]["rot"].update(dims=34), ValueError),
     (lambda r: r.pop("width"), KeyError),
@@ -154,3 +161,19 @@ def test_oracle_is_causal_and_shared_layers_share(tmp_path):
     f = fx.oracle(folder)
     ids = [3, 14, 15, 92, 65, 35, 89, 79, 32, 38]
     assert torch.allclose(f(ids)[:6], f(ids[:6]), atol=1e-10)
+
+
+def test_preset_writes_a_folder_that_loads_back(tmp_path):
+    from miniserve_b200.config import preset
+    from miniserve_b200.config.registry import load_config_dict
+    from miniserve_b200.weights import load_weights
+    from miniserve_b200.weights.random_init import write_model_folder
+
+    folder = write_model_folder(tmp_path / "m", preset("fekulix-tiny"), seed=3, std=0.1)
+    _, _, spec = resolve(load_config_dict(folder), folder)
+    assert [e.layer for e in spec.run_order] == [0, 1, 0, 1]
+    model = DecoderModel(spec, torch.float32, "cpu")
+    tensors = load_weights(folder, model.weight_decls(), torch.float32, "cpu", rules=spec.checkpoint_rules, stacks=model.weight_stacks())
+    model.bind(tensors)
+    logits = fx.oracle(folder)([5, 17, 3])
+    assert logits.shape == (3, 503) and torch.isfinite(logits).all()

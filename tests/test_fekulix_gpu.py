@@ -18,8 +18,7 @@ from tests.plain import fekulix_plain as plain
 
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda")
-F32, BF16 = 2e-5, 1e-1  # logits: distance over their spread (rel_err). bfloat16: rounding alone reaches 0.05 at the worst
-# position of these models (peaked attention, narrow widths); a lost key, a stale state or a wrong slot moves logits by 0.3 to 1
+F32, BF16 = 2e-5, 1e-1  # logits: distance over their spread (rel_err); bfloat16: see the model fixture
 
 
 def _ids(n, vocab, seed):
@@ -220,16 +219,20 @@ def test_gated_delta_rule(dtype, heads, groups, dk, dv, taps, ranks):
 
 
 # --------------------------------------------------------------------------- whole models
-@pytest.fixture(scope="module", params=["a", "b"])
+@pytest.fixture(scope="module", params=["a", "b", "c"])
 def model(request, tmp_path_factory):
-    raw = fx.config_a() if request.param == "a" else fx.config_b()
-    folder = fx.write_model(tmp_path_factory.mktemp("fekulix_" + request.param), raw, seed=11 if request.param == "a" else 12)
-    return dict(folder=folder, raw=raw, oracle=fx.oracle(folder), page=16 if request.param == "a" else 8)
+    raw = dict(a=fx.config_a, b=fx.config_b, c=fx.config_c)[request.param]()
+    folder = fx.write_model(tmp_path_factory.mktemp("fekulix_" + request.param), raw, seed=dict(a=11, b=12, c=13)[request.param])
+    # bfloat16: the engine may be as far from the float64 truth as rounding alone takes the oracle (times 2.5: it
+    # rounds in more places than the products), and at least 0.1; a lost key, a stale state or a wrong slot costs 0.3 to 1
+    noise = fx.rounding_noise(folder, _ids(90, raw["vocab"], 20))
+    return dict(folder=folder, raw=raw, oracle=fx.oracle(folder), page=dict(a=16, b=8, c=32)[request.param],
+                tol={"float32": F32, "bfloat16": max(BF16, 2.5 * noise)})
 
 
-@pytest.mark.parametrize("dtype, tol", [("float32", F32), ("bfloat16", BF16)])
-def test_whole_decoded_and_in_portions(model, dtype, tol):
-    vocab = model["raw"]["vocab"]
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_decoded_and_in_portions(model, dtype):
+    vocab, tol = model["raw"]["vocab"], model["tol"][dtype]
     run = fx.Runner(model["folder"], dtype, max_tokens=256, page_size=model["page"])
     for n, seed in ((1, 1), (2, 2), (37, 3), (150, 4)):
         ids = _ids(n, vocab, seed)
@@ -241,12 +244,12 @@ def test_whole_decoded_and_in_portions(model, dtype, tol):
         assert run.cache.is_idle()
 
 
-@pytest.mark.parametrize("dtype, tol", [("float32", F32), ("bfloat16", BF16)])
-def test_mixed_batches_reuse_pages_and_slots(model, dtype, tol):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_batches_reuse_pages_and_slots(model, dtype):
     """Up to four live requests, portions of some beside single tokens of others, a pool that holds
     only what is live: every page and slot is used by several requests in turn (pages are filled
     with NaN when given back, state slots keep the old request's state)."""
-    vocab = model["raw"]["vocab"]
+    vocab, tol = model["raw"]["vocab"], model["tol"][dtype]
     seqs = {f"r{i}": _ids(n, vocab, 20 + i) for i, n in enumerate([90, 5, 64, 33, 1, 120, 17, 48])}
     want = {k: model["oracle"](v) for k, v in seqs.items()}
     run = fx.Runner(model["folder"], dtype, max_tokens=4 * 128, page_size=model["page"], max_requests=4)
