@@ -207,6 +207,120 @@ decay_scan_kernel(float* __restrict__ o_out,   // [T, H, dv]
   }
 }
 
+// ---------------------------------------------------------------- the decay rule over segments of a long row
+// The decay rule is linear in the state with a diagonal factor: S_t = a_t (.) S_(t-1) + k_t v_t^T. So a long row
+// is cut into P segments that are walked at the same time, each from a zero state (decay_scan_kernel over the
+// segments as if they were rows, its end states going to scratch slots). With c_t the product of the decays
+// from the segment's first token to t (per key channel) and S0 the state before the segment,
+//     o_t = o_t(from zero) + S0^T (q_t (.) c_t),     S0(next segment) = c_last (.) S0 + S_end(from zero),
+// which is what the three kernels below add: the running products, the states before every segment (a
+// short walk over the P segments of a row; it also leaves the row's final state in the request's slot), and
+// the missing part of every output. All of it in float32.
+
+// seg_cu[r * P + s]: first token of segment s of row r (segments of ceil(len / P) tokens; the last ones may be empty)
+__global__ void segment_setup_kernel(int* __restrict__ seg_cu, int* __restrict__ seg_zero, int* __restrict__ seg_slot,
+                                     const int* __restrict__ cu_q, int num_rows, int P) {
+  pdl_prologue();
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx > num_rows * P) return;
+  if (idx == num_rows * P) {
+    seg_cu[idx] = cu_q[num_rows];
+    return;
+  }
+  const int r = idx / P, sgm = idx - r * P;
+  const int t0 = cu_q[r], len = cu_q[r + 1] - t0;
+  const int per = (len + P - 1) / P;
+  seg_cu[idx] = t0 + min(len, sgm * per);
+  seg_zero[idx] = 0;
+  seg_slot[idx] = idx;
+}
+
+// c[t, ch] = product of decay[s, ch] over the tokens s of t's segment up to and including t. One thread per (segment, channel).
+__global__ void segment_cumprod_kernel(float* __restrict__ c, const float* __restrict__ decay, int ld_decay,
+                                       const int* __restrict__ seg_cu, int num_segments, int width) {
+  pdl_prologue();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)num_segments * width) return;
+  const int sg = (int)(idx / width), ch = (int)(idx - (long long)sg * width);
+  float run = 1.f;
+  const int t_end = seg_cu[sg + 1];
+#pragma unroll 8
+  for (int t = seg_cu[sg]; t < t_end; ++t) {
+    run *= decay[(size_t)t * ld_decay + ch];
+    c[(size_t)t * width + ch] = run;
+  }
+}
+
+// before[seg] = the state before segment seg; the row's slot gets the state after its last segment.
+// One thread per (row, head, column, key channel); states are [.., H, dv, dk].
+__global__ void segment_combine_kernel(float* __restrict__ state, const float* __restrict__ ends, float* __restrict__ before,
+                                       const float* __restrict__ c, const int* __restrict__ seg_cu,
+                                       const int* __restrict__ q_start, const int* __restrict__ state_slot, int num_rows, int P,
+                                       int H, int dk, int dv) {
+  pdl_prologue();
+  const long long per_row = (long long)H * dv * dk;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= num_rows * per_row) return;
+  const int r = (int)(idx / per_row);
+  const long long e = idx - r * per_row;  // (h, j, i) flattened as in the state
+  const int i = (int)(e % dk), h = (int)(e / ((long long)dv * dk));
+  float* slot = state + (size_t)state_slot[r] * per_row + e;
+  float S = q_start[r] == 0 ? 0.f : *slot;
+  for (int sgm = 0; sgm < P; ++sgm) {
+    const int sg = r * P + sgm;
+    before[(size_t)sg * per_row + e] = S;
+    const int first = seg_cu[sg], end = seg_cu[sg + 1];
+    if (end > first) S = c[(size_t)(end - 1) * H * dk + (size_t)h * dk + i] * S + ends[(size_t)sg * per_row + e];
+  }
+  *slot = S;
+}
+
+// o[t, h, j] += sum_i (q[t, i] q_scale c[t, h, i]) before[seg(t)][h, j, i]. One CTA per (segment, head, run of
+// FIX_RUN tokens): the tokens' scaled queries in shared memory, then tile after tile of the state's columns
+// (rows padded by one word).
+constexpr int FIX_RUN = 32, FIX_THREADS = 256;
+template <typename TIn>
+__global__ void __launch_bounds__(FIX_THREADS)
+segment_fixup_kernel(float* __restrict__ o, const TIn* __restrict__ q, int ld_q, int qk_group, const float* __restrict__ c,
+                     const float* __restrict__ before, const int* __restrict__ seg_cu, const int* __restrict__ q_start, int P,
+                     int H, int dk, int dv, int cols, float q_scale) {
+  extern __shared__ float fix_smem[];
+  pdl_prologue();
+  const int sg = blockIdx.x, h = blockIdx.y;
+  const int t0 = seg_cu[sg] + blockIdx.z * FIX_RUN, end = min(seg_cu[sg + 1], t0 + FIX_RUN);
+  if (end <= t0) return;
+  if (sg % P == 0 && q_start[sg / P] == 0) return;  // the first segment of a sequence: nothing came before
+  float* st = fix_smem;                    // [cols][dk + 1]
+  float* qc = st + (size_t)cols * (dk + 1);  // [FIX_RUN][dk]
+  const int qk_head = h / qk_group;
+  const int n = end - t0;
+  for (int idx = threadIdx.x; idx < n * dk; idx += FIX_THREADS) {
+    const int tt = idx / dk, i = idx - tt * dk;
+    const size_t tok = (size_t)(t0 + tt);
+    qc[idx] = Elem<TIn>::load(q + tok * ld_q + (size_t)qk_head * dk + i) * q_scale * c[tok * H * dk + (size_t)h * dk + i];
+  }
+  for (int j0 = 0; j0 < dv; j0 += cols) {
+    const int ncols = min(cols, dv - j0);
+    const float* src = before + (((size_t)sg * H + h) * dv + j0) * dk;
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < ncols * dk; idx += FIX_THREADS) st[(idx / dk) * (dk + 1) + idx % dk] = src[idx];
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n * ncols; idx += FIX_THREADS) {
+      const int tt = idx / ncols, j = idx - tt * ncols;
+      const float* sj = st + (size_t)j * (dk + 1);
+      const float* qt = qc + (size_t)tt * dk;
+      float a4[4] = {0.f, 0.f, 0.f, 0.f};
+      int i = 0;
+      for (; i + 4 <= dk; i += 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) a4[e] = fmaf(qt[i + e], sj[i + e], a4[e]);
+      }
+      for (; i < dk; ++i) a4[0] = fmaf(qt[i], sj[i], a4[0]);
+      o[((size_t)(t0 + tt) * H + h) * dv + j0 + j] += (a4[0] + a4[1]) + (a4[2] + a4[3]);
+    }
+  }
+}
+
 // Short causal convolution over time per channel, then SiLU, then (for the first `unit_heads` heads of
 // `dk` channels) division by the head's Euclidean length: y / sqrt(sum y^2 + unit_eps). The heads after
 // those have `dv` channels and are not normalised. Channels are columns [0, C) of the projection's rows;
@@ -321,6 +435,9 @@ int launch_scan_kpt(float* o_out, float* state, const void* q, int ld_q, const v
   const int per_token = (3 * dkp + cols + 1) * (int)sizeof(float);
   int chunk = (40 * 1024) / per_token;
   chunk = chunk > 32 ? 32 : (chunk < 1 ? 1 : chunk);
+  // many CTAs (rows cut into segments, large batches): short chunks, so that many of them fit an SM and
+  // one CTA's staging hides behind the others' walks
+  if ((long long)num_rows * H * ((dv + cols - 1) / cols) >= 8LL * sm_count && chunk > 8) chunk = 8;
   const size_t smem = (size_t)chunk * per_token;
   auto kernel = decay_scan_kernel<TIn, TZ, DELTA, SCAN_KPT>;
   const dim3 grid(num_rows, H, (dv + cols - 1) / cols);
@@ -334,13 +451,14 @@ int launch_scan_kpt(float* o_out, float* state, const void* q, int ld_q, const v
   return 0;
 }
 
-// A token's work in a warp is one dependent chain, so a launch is as fast as its warps are many: with few
-// (request, head) pairs a column is spread over more threads (4 or 8 channels each instead of 16), at the
-// price of a longer exchange within the lane group. The sums' order follows the channels a thread holds,
-// so the choice must not depend on the batch: it follows the heads' sizes alone.
+// A token's work in a warp is one dependent chain, so a launch with few warps is as fast as its warps are many:
+// with few (row, head) pairs a column is spread over more threads (4 or 8 channels each instead of 16), at
+// the price of more instructions per state entry and a longer exchange within the lane group; a launch
+// that fills the GPU anyway (a batch of decoding rows, rows cut into segments) keeps 16 channels a thread.
+// The order of a sum over key channels follows the choice, so results differ between launches by rounding.
 template <typename TIn, typename TZ, bool DELTA, typename... Args>
-int launch_scan(int H, int dk, int dv, Args... args) {
-  const long long threads16 = (long long)H * dv * ((dk + 15) / 16);  // of one request, at 16 channels a thread
+int launch_scan(int num_rows, int H, int dk, int dv, Args... args) {
+  const long long threads16 = (long long)num_rows * H * dv * ((dk + 15) / 16);  // at 16 channels a thread
   const int sm_count = scan_sm_count();
   if (dk <= 32 * 4 && threads16 * 4 <= 128LL * sm_count) return launch_scan_kpt<TIn, TZ, DELTA, 4>(args...);
   if (dk <= 32 * 8 && threads16 * 2 <= 128LL * sm_count) return launch_scan_kpt<TIn, TZ, DELTA, 8>(args...);
@@ -364,7 +482,7 @@ MS_EXPORT int ms_decay_scan(float* o_out, float* state, const void* q, int ld_q,
   MS_CHECK_ARG(!delta || beta != nullptr, "decay_scan: the delta rule needs beta");
   MS_CHECK_ARG(!z_is_decay || z_dtype == MS_F32, "decay_scan: decays worked out beforehand are float32");
 #define MS_SCAN(TIN, TZZ, D)                                                                                                  \
-  return launch_scan<TIN, TZZ, D>(H, dk, dv, o_out, state, q, ld_q, k, ld_k, qk_group, v, ld_v, z, ld_z, z_bias, decay_coef, z_sign, z_is_decay, \
+  return launch_scan<TIN, TZZ, D>(num_rows, H, dk, dv, o_out, state, q, ld_q, k, ld_k, qk_group, v, ld_v, z, ld_z, z_bias, decay_coef, z_sign, z_is_decay, \
                                   beta, ld_beta, cu_q, q_start, state_slot, num_rows, H, dk, dv, q_scale, stream)
   if (in_dtype == MS_F32 && z_dtype == MS_F32) {
     if (delta) MS_SCAN(float, float, true);
@@ -397,6 +515,45 @@ MS_EXPORT int ms_decay_from_logits(float* out, const void* z, int ld_z, const fl
   else
     MS_LAUNCH(decay_from_logits_kernel<__nv_bfloat16>, blocks, 256, 0, stream, out, (const __nv_bfloat16*)z, ld_z, z_bias, decay_coef,
               z_sign, (const __nv_bfloat16*)beta, ld_beta, items, H, dk);
+  return 0;
+}
+
+MS_EXPORT int ms_segment_setup(int* seg_cu, int* seg_zero, int* seg_slot, const int* cu_q, int num_rows, int P, cudaStream_t stream) {
+  if (num_rows == 0) return 0;
+  MS_CHECK_ARG(P >= 1, "segment_setup: %d segments", P);
+  MS_LAUNCH(segment_setup_kernel, (num_rows * P + 1 + 127) / 128, 128, 0, stream, seg_cu, seg_zero, seg_slot, cu_q, num_rows, P);
+  return 0;
+}
+
+// What the decay rule over segments adds to decay_scan run over the segments as rows (see above). decay [T, .] float32
+// (ms_decay_from_logits), c [T, H * dk] and before [rows * P, H, dv, dk] scratch, ends [rows * P, H, dv, dk] the scan's end states.
+MS_EXPORT int ms_segment_finish(float* o, float* state, const float* ends, float* before, float* c, const float* decay, int ld_decay,
+                                const void* q, int ld_q, int qk_group, const int* seg_cu, const int* q_start, const int* state_slot,
+                                int num_rows, int num_tokens, int P, int H, int dk, int dv, float q_scale, int in_dtype, cudaStream_t stream) {
+  if (num_rows == 0) return 0;
+  const int segments = num_rows * P, width = H * dk;
+  {
+    const long long items = (long long)segments * width;
+    MS_LAUNCH(segment_cumprod_kernel, (unsigned)((items + 127) / 128), 128, 0, stream, c, decay, ld_decay, seg_cu, segments, width);
+  }
+  {
+    const long long items = (long long)num_rows * H * dv * dk;
+    MS_LAUNCH(segment_combine_kernel, (unsigned)((items + 255) / 256), 256, 0, stream, state, ends, before, c, seg_cu, q_start,
+              state_slot, num_rows, P, H, dk, dv);
+  }
+  int cols = dv;
+  while (cols > 1 && ((size_t)cols * (dk + 1) + (size_t)FIX_RUN * dk) * sizeof(float) > 40 * 1024) cols = (cols + 1) / 2;
+  const size_t smem = ((size_t)cols * (dk + 1) + (size_t)FIX_RUN * dk) * sizeof(float);
+  MS_CHECK_ARG(smem <= 48 * 1024, "segment_finish: a key size of %d does not fit shared memory", dk);
+  // a segment has at most ceil(tokens of the step / P) tokens
+  const int longest = (num_tokens + P - 1) / P;
+  const dim3 grid(segments, H, (longest + FIX_RUN - 1) / FIX_RUN);
+  if (in_dtype == MS_F32)
+    MS_LAUNCH(segment_fixup_kernel<float>, grid, FIX_THREADS, smem, stream, o, (const float*)q, ld_q, qk_group, c, before, seg_cu, q_start,
+              P, H, dk, dv, cols, q_scale);
+  else
+    MS_LAUNCH(segment_fixup_kernel<__nv_bfloat16>, grid, FIX_THREADS, smem, stream, o, (const __nv_bfloat16*)q, ld_q, qk_group, c, before,
+              seg_cu, q_start, P, H, dk, dv, cols, q_scale);
   return 0;
 }
 

@@ -115,6 +115,8 @@ def decay_scan(o_out, state, q, k, v, z, z_bias, decay_coef, z_sign: float, beta
     groups = q.shape[1] // dk
     assert q.shape == (t, groups * dk) and k.shape == q.shape and v.shape == (t, heads * dv) and z.shape == (t, heads * dk)
     assert q.dtype == k.dtype == v.dtype and (beta is None or beta.dtype == z.dtype)
+    if not delta and not ctx.decode_only and t >= SEGMENT_MIN_TOKENS and SEGMENTS > 1:
+        return _decay_scan_segmented(o_out, state, q, k, v, z, z_bias, decay_coef, z_sign, ctx, heads, dk, dv, q_scale)
     ready = 0
     if not ctx.decode_only:
         # a prompt portion: exponentials and logarithms for all tokens at once, not inside the serial walk
@@ -153,6 +155,45 @@ def conv_state_update(conv_state, x, ctx, taps: int) -> None:
     native.kernel_check(native.kernels().ms_conv_state_update(
         _ptr(conv_state), _ptr(x), _rows(x), _ptr(ctx.cu_q), _ptr(ctx.q_start), _ptr(ctx.state_slot), ctx.num_rows, x.shape[1],
         taps, _dt(x.dtype), ctx.stream))
+
+
+# The decay rule is linear in the state with a diagonal factor, so the rows of a step with many tokens are cut into
+# SEGMENTS pieces that are walked at the same time (``csrc/recurrence.cu``). Whether a step is cut follows from its
+# number of tokens alone (what a captured graph is keyed by), never from how the tokens are shared among rows.
+SEGMENTS = 8
+SEGMENT_MIN_TOKENS = 512
+
+
+def _decay_scan_segmented(o_out, state, q, k, v, z, z_bias, decay_coef, z_sign, ctx, heads, dk, dv, q_scale) -> None:
+    from types import SimpleNamespace
+
+    t, dev, p, rows = o_out.shape[0], o_out.device, SEGMENTS, ctx.num_rows
+    lib = native.kernels()
+    key = ("scan.segments", p)
+    seg = ctx.step_cache.get(key) if hasattr(ctx, "step_cache") else None
+    if seg is None:  # the same for every layer of the step
+        ints = torch.empty(3 * rows * p + 1, dtype=torch.int32, device=dev)
+        seg = (ints[:rows * p + 1], ints[rows * p + 1:2 * rows * p + 1], ints[2 * rows * p + 1:])
+        native.kernel_check(lib.ms_segment_setup(_ptr(seg[0]), _ptr(seg[1]), _ptr(seg[2]), _ptr(ctx.cu_q), rows, p, ctx.stream))
+        if hasattr(ctx, "step_cache"):
+            ctx.step_cache[key] = seg
+    seg_cu, seg_zero, seg_slot = seg
+    decay = ctx.buffer("scan.decay", (t, heads * dk), torch.float32, dev)
+    native.kernel_check(lib.ms_decay_from_logits(_ptr(decay), _ptr(z), _rows(z), _ptr(z_bias), _ptr(decay_coef), float(z_sign), None, 0,
+                                                 t, heads, dk, _dt(z.dtype), ctx.stream))
+    ends = ctx.buffer("scan.ends", (rows * p, heads, dv, dk), torch.float32, dev)
+    before = ctx.buffer("scan.before", (rows * p, heads, dv, dk), torch.float32, dev)
+    cum = ctx.buffer("scan.cum", (t, heads * dk), torch.float32, dev)
+    pieces = SimpleNamespace(cu_q=seg_cu, q_start=seg_zero, state_slot=seg_slot, num_rows=rows * p, stream=ctx.stream)
+    groups = q.shape[1] // dk
+    native.kernel_check(lib.ms_decay_scan(
+        _ptr(o_out), _ptr(ends), _ptr(q), _rows(q), _ptr(k), _rows(k), heads // groups, _ptr(v), _rows(v), _ptr(decay), _rows(decay),
+        _ptr(z_bias), _ptr(decay_coef), float(z_sign), 1, None, 0, _ptr(pieces.cu_q), _ptr(pieces.q_start), _ptr(pieces.state_slot),
+        pieces.num_rows, heads, dk, dv, float(q_scale), 0, _dt(q.dtype), 0, ctx.stream))
+    native.kernel_check(lib.ms_segment_finish(
+        _ptr(o_out), _ptr(state), _ptr(ends), _ptr(before), _ptr(cum), _ptr(decay), _rows(decay), _ptr(q), _rows(q), heads // groups,
+        _ptr(seg_cu), _ptr(ctx.q_start), _ptr(ctx.state_slot), rows, t, p, heads, dk, dv, float(q_scale), _dt(q.dtype), ctx.stream),
+        launches=3)
 
 
 GATE_KINDS = {"silu": 0, "sigmoid": 1}

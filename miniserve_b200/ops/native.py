@@ -118,6 +118,8 @@ def kernels():
     _declare(lib, "ms_qkv_prepare", [_p] * 4 + [_i] * 4 + [_p] * 7 + [_i] * 8 + [_f, _i, _i, _p, _i, _p])
     _declare(lib, "ms_decay_scan", [_p, _p, _p, _i, _p, _i, _i, _p, _i, _p, _i, _p, _p, _f, _i, _p, _i, _p, _p, _p,
                                     _i, _i, _i, _i, _f, _i, _i, _i, _p])
+    _declare(lib, "ms_segment_setup", [_p, _p, _p, _p, _i, _i, _p])
+    _declare(lib, "ms_segment_finish", [_p, _p, _p, _p, _p, _p, _i, _p, _i, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p])
     _declare(lib, "ms_decay_from_logits", [_p, _p, _i, _p, _p, _f, _p, _i, _i, _i, _i, _i, _p])
     _declare(lib, "ms_conv_silu_unit", [_p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p])
     _declare(lib, "ms_conv_state_update", [_p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p])

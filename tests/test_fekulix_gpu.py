@@ -195,6 +195,31 @@ def test_decay_linear_attention(dtype, heads, dk, dv, rank):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, dk, dv", [(2, 24, 40), (1, 20, 136)])
+def test_decay_linear_attention_over_segments_of_a_long_portion(dtype, heads, dk, dv):
+    """A step of 512 tokens or more walks every row in eight segments at once and mends the outputs and the
+    state afterwards: against the token-by-token oracle, whole, behind an earlier portion (a state to start
+    from), beside a short row (segments that are empty), and then decoded on from the state it left."""
+    c = dict(heads=heads, dim=dk, vdim=dv, tau=3.0)
+    spec = PartSpec("decay_linear_attention", dict(hidden=48, heads=heads, key_dim=dk, value_dim=dv, tau=3.0, decay_rank=8, eps=1e-5,
+                                                   names=dict(q="q", k="k", v="v", g="g", o="o", norm="norm", a1="a1", a2="a2", a_bias="a2.b")))
+    part = build_part("mixer", spec, BuildEnv(dtype, DEV))
+    w = _bind(part, dtype)
+    n = 700
+    x = torch.randn(n, 48, device=DEV).to(dtype)
+    ref = plain.linear_branch(x.double().cpu(), lambda name: w[name], c, 1e-5)
+    views = _state_views(part)
+    _close(_portions(part, views, x, (n,), 1, dtype), ref, dtype, 3.0)
+    _close(_portions(part, views, x, (37, 600, 2) + (1,) * n, 1, dtype), ref, dtype, 3.0)
+    _, ctx = _ctx([(0, 5), (0, 690)], dtype=dtype, slots=[4, 0])
+    both = part.forward(torch.cat((x[:5], x[:690])), ctx, views)
+    _close(both[:5], ref[:5], dtype, 3.0)
+    _close(both[5:], ref[:690], dtype, 3.0)
+    _, ctx = _ctx([(690, 10)], dtype=dtype, slots=[0])
+    _close(part.forward(x[690:].contiguous(), ctx, views), ref[690:], dtype, 3.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads, groups, dk, dv, taps, ranks", [(4, 2, 16, 24, 3, (8, 16)), (2, 2, 40, 12, 2, (3, 7)),
                                                                (3, 1, 8, 16, 1, (8, 8)), (2, 1, 32, 72, 5, (4, 4))])
 def test_gated_delta_rule(dtype, heads, groups, dk, dv, taps, ranks):
