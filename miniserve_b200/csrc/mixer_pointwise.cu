@@ -88,6 +88,116 @@ __global__ void head_gate_kernel(T* __restrict__ out, int ld_out, const T* __res
   Elem<T>::store(out + t * ld_out + (size_t)h * dv + c, g * Elem<T>::load(attn + (t * nq + h) * d_pad + c));
 }
 
+// The same for bfloat16 rows that start on 16 bytes and value sizes that are multiples of 8: one warp per
+// (token, head), the gate worked out once, eight values per lane and trip.
+__global__ void head_gate_bf16x8_kernel(__nv_bfloat16* __restrict__ out, int ld_out, const __nv_bfloat16* __restrict__ attn,
+                                        const __nv_bfloat16* __restrict__ gate, int ld_gate, long long pairs, int nq, int d_pad,
+                                        int dv, float scale) {
+  pdl_prologue();
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= pairs) return;
+  const long long t = item / nq;
+  const int h = (int)(item - t * nq);
+  float g = scale;
+  if (gate) g *= 1.0f / (1.0f + expf(-__bfloat162float(gate[t * ld_gate + h])));
+  const __nv_bfloat16* src = attn + item * d_pad;
+  __nv_bfloat16* dst = out + t * ld_out + (size_t)h * dv;
+  for (int c = lane * 8; c < dv; c += 256) {
+    float v[8];
+    bf16x8_to_float(*reinterpret_cast<const uint4*>(src + c), v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] *= g;
+    *reinterpret_cast<uint4*>(dst + c) = float_to_bf16x8(v);
+  }
+}
+
+// bfloat16, adjacent rotation pairs, sizes that are multiples of 8, rows on 16 bytes: a lane holds eight
+// consecutive channels (four rotation pairs), so the rotation needs no exchange; one warp per (token, head).
+__global__ void qkv_prepare_bf16x8_kernel(
+    __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool,
+    const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ q_norm_w,
+    const float* __restrict__ k_norm_w, const float* __restrict__ cos_sin, const int* __restrict__ positions,
+    const int* __restrict__ row_of_token, const int* __restrict__ page_indptr, const int* __restrict__ page_indices,
+    int num_tokens, int nq, int nkv, int dk, int dv, int d_pad, int rot, float eps, int page_shift, int num_pages,
+    int* __restrict__ status) {
+  pdl_prologue();
+  const int lane = threadIdx.x & 31;
+  const int heads_total = nq + 2 * nkv;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long long)num_tokens * heads_total) return;
+  const int t = (int)(item / heads_total);
+  const int h = (int)(item - (long long)t * heads_total);
+  const __nv_bfloat16* row_in = proj + (size_t)t * ld;
+  const int pos = positions[t];
+  const __nv_bfloat16* src;
+  __nv_bfloat16* dst;
+  const float* nw = nullptr;
+  bool is_v = false;
+  if (h < nq) {
+    src = row_in + q_off + (size_t)h * dk;
+    dst = q_out + ((size_t)t * nq + h) * d_pad;
+    nw = q_norm_w;
+  } else {
+    const int kvh = (h - nq) % nkv;
+    is_v = (h - nq) >= nkv;
+    const int row = row_of_token[t];
+    const int page_size = 1 << page_shift;
+    const int page = page_indices[page_indptr[row] + (pos >> page_shift)];
+    if (page < 0) {
+      if (lane == 0) atomicExch(status, 2);
+      return;
+    }
+    MS_DEBUG_ONLY(if (page >= num_pages || row < 0) {
+      if (lane == 0) atomicExch(status, 5);
+      return;
+    })
+    dst = (is_v ? v_pool : k_pool) + (((size_t)page * nkv + kvh) * page_size + (pos & (page_size - 1))) * d_pad;
+    src = is_v ? row_in + v_off + (size_t)kvh * dv : row_in + k_off + (size_t)kvh * dk;
+    nw = k_norm_w;
+  }
+  const int own = is_v ? dv : dk;
+  // (a head of up to 256 channels: one trip; wider heads take more)
+  float ss = 0.f;
+  if (!is_v && nw) {
+    for (int c = lane * 8; c < dk; c += 256) {
+      float v[8];
+      bf16x8_to_float(*reinterpret_cast<const uint4*>(src + c), v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+    }
+    ss = warp_sum(ss);
+  }
+  const float inv = (!is_v && nw) ? 1.0f / sqrtf(ss / (float)dk + eps) : 1.f;
+  const int half = rot >> 1;
+  for (int c = lane * 8; c < d_pad; c += 256) {
+    float v[8];
+    if (c < own) {
+      bf16x8_to_float(*reinterpret_cast<const uint4*>(src + c), v);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = 0.f;
+    }
+    if (!is_v && c < dk) {
+      if (nw) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = (v[e] * inv) * nw[c + e];
+      }
+#pragma unroll
+      for (int e = 0; e < 8; e += 2) {
+        const int j = (c + e) >> 1;
+        if (j < half) {
+          const float cs = cos_sin[(size_t)t * rot + j], sn = cos_sin[(size_t)t * rot + half + j];
+          const float a = v[e], b = v[e + 1];
+          v[e] = a * cs - b * sn;
+          v[e + 1] = b * cs + a * sn;
+        }
+      }
+    }
+    *reinterpret_cast<uint4*>(dst + c) = float_to_bf16x8(v);
+  }
+}
+
 // One warp per (token, head) over the nq query heads, nkv key heads and nkv value heads of a token.
 template <typename T>
 __global__ void qkv_prepare_kernel(
@@ -175,6 +285,9 @@ __global__ void qkv_prepare_kernel(
 
 using namespace ms;
 
+MS_DEFINE_LAST_ERROR(ms_mixers_last_error)
+MS_DEFINE_PDL_SWITCH(ms_mixers_set_pdl)
+
 MS_EXPORT int ms_add_dyt(void* out, float* residual, const void* delta, const float* w, const float* b, const float* alpha,
                          const int* rows, int n, int hidden, int write_residual, int dtype, cudaStream_t stream) {
   if (n == 0) return 0;
@@ -225,6 +338,12 @@ MS_EXPORT int ms_head_gate(void* out, int ld_out, const void* attn, const void* 
   MS_CHECK_ARG(nq > 0 && dv > 0 && dv <= d_pad, "head_gate: bad sizes nq=%d dv=%d D=%d", nq, dv, d_pad);
   const long long items = (long long)num_tokens * nq * dv;
   const unsigned blocks = (unsigned)((items + 255) / 256);
+  if (dtype == MS_BF16 && dv % 8 == 0 && d_pad % 8 == 0 && ld_out % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)attn % 16 == 0) {
+    const long long pairs = (long long)num_tokens * nq;
+    MS_LAUNCH(head_gate_bf16x8_kernel, (unsigned)((pairs + 7) / 8), 256, 0, stream, (__nv_bfloat16*)out, ld_out,
+              (const __nv_bfloat16*)attn, (const __nv_bfloat16*)gate, ld_gate, pairs, nq, d_pad, dv, scale);
+    return 0;
+  }
   if (dtype == MS_F32)
     MS_LAUNCH(head_gate_kernel<float>, blocks, 256, 0, stream, (float*)out, ld_out, (const float*)attn, (const float*)gate, ld_gate,
               items, nq, d_pad, dv, scale, gate != nullptr);
@@ -250,6 +369,14 @@ MS_EXPORT int ms_qkv_prepare(void* q_out, void* k_pool, void* v_pool, const void
   const long long items = (long long)num_tokens * (nq + 2 * nkv);
   const int warps = 8;
   const unsigned blocks = (unsigned)((items + warps - 1) / warps);
+  if (dtype == MS_BF16 && (adjacent || rot == 0) && dk % 8 == 0 && dv % 8 == 0 && d_pad % 8 == 0 && ld % 8 == 0 && q_off % 8 == 0 &&
+      k_off % 8 == 0 && v_off % 8 == 0 && (uintptr_t)proj % 16 == 0 && (uintptr_t)q_out % 16 == 0 && (uintptr_t)k_pool % 16 == 0 &&
+      (uintptr_t)v_pool % 16 == 0) {
+    MS_LAUNCH(qkv_prepare_bf16x8_kernel, blocks, warps * 32, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
+              (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)proj, ld, q_off, k_off, v_off, q_norm_w, k_norm_w, cos_sin, positions,
+              row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, dk, dv, d_pad, rot, eps, page_shift, num_pages, status);
+    return 0;
+  }
   if (dtype == MS_F32)
     MS_LAUNCH(qkv_prepare_kernel<float>, blocks, warps * 32, 0, stream, (float*)q_out, (float*)k_pool, (float*)v_pool,
               (const float*)proj, ld, q_off, k_off, v_off, q_norm_w, k_norm_w, cos_sin, positions, row_of_token, page_indptr,

@@ -110,6 +110,18 @@ def kernels():
     _declare(lib, "ms_gemm_f32", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p])
     _declare(lib, "ms_attention_rowwise",
              [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p, _i, _p])
+    _declare(lib, "ms_nucleus_bytes", [])
+    _declare(lib, "ms_sample_scratch_bytes", [_i, _i], _ll)
+    _declare(lib, "ms_sample", [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p])
+    return lib
+
+
+@lru_cache(maxsize=None)
+def mixers():
+    lib = ctypes.CDLL(str(build.ensure_built(build.MIXERS)))
+    _declare(lib, "ms_mixers_last_error", [], c_char_p)
+    _declare(lib, "ms_mixers_set_pdl", [_i], None)
+    lib.ms_mixers_set_pdl(int(pdl_enabled()))
     _declare(lib, "ms_add_dyt", [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p])
     _declare(lib, "ms_gelu_tanh", [_p, _p, _ll, _i, _p])
     _declare(lib, "ms_scale_f32", [_p, _f, _ll, _p])
@@ -124,10 +136,11 @@ def kernels():
     _declare(lib, "ms_conv_silu_unit", [_p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p])
     _declare(lib, "ms_conv_state_update", [_p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p])
     _declare(lib, "ms_head_norm_gate", [_p, _i, _p, _p, _p, _i, _i, _i, _i, _f, _f, _i, _i, _p])
-    _declare(lib, "ms_nucleus_bytes", [])
-    _declare(lib, "ms_sample_scratch_bytes", [_i, _i], _ll)
-    _declare(lib, "ms_sample", [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p])
     return lib
+
+
+def mixers_check(rc: int, launches: int = 1) -> None:
+    kernel_check(rc, lib=mixers() if rc else None, errfn="ms_mixers_last_error", launches=launches)
 
 
 @lru_cache(maxsize=None)
