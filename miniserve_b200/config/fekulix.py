@@ -103,4 +103,7 @@ def complete_from_shapes(raw: Mapping[str, Any], shapes: Mapping[str, tuple]) ->
                 name = f"l{src}.mix.{tensor}"
                 if key not in m and name in shapes:
                     m[key] = int(shapes[name][0])
+            name = f"l{src}.mix.q.conv"
+            if "conv" not in m and name in shapes:  # the taps are the convolution tensor's second dimension
+                m["conv"] = int(shapes[name][1])
     return raw

@@ -83,6 +83,8 @@ def test_ranks_come_from_the_checkpoint(tmp_path):
     _, _, spec = resolve(stored, folder)
     assert spec.layers[0].mixer["branches"][1][1]["decay_rank"] == 5
     assert (spec.layers[1].mixer["decay_rank"], spec.layers[1].mixer["gate_rank"]) == (3, 7)
+    del stored["layers"][1]["mixer"]["conv"]  # the taps, too, are a tensor's shape if config.json does not say
+    assert resolve(stored, folder)[2].layers[1].mixer["conv"] == 2
     assert architecture_of({"architectures": ["Qwen3ForCausalLM"]}).name == "Qwen3ForCausalLM"
 
 
