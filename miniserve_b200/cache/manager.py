@@ -42,7 +42,7 @@ class CacheGroup:
         return self.allocator.num_blocks
 
     def bytes_per_token(self, itemsize: int) -> int:
-        return 2 * len(self.entries) * self.need.kv_heads * self.need.head_dim * itemsize
+        return (2 if self.need.values else 1) * len(self.entries) * self.need.kv_heads * self.need.head_dim * itemsize
 
 
 @dataclass
@@ -158,7 +158,7 @@ class CacheManager:
                 shape = (len(grp.entries), grp.allocator.num_blocks + 1, grp.need.kv_heads, page_size, grp.need.head_dim)
                 fill = float("nan") if poison else 0.0
                 grp.k = torch.full(shape, fill, dtype=dtype, device=self.device)
-                grp.v = torch.full(shape, fill, dtype=dtype, device=self.device)
+                grp.v = torch.full(shape, fill, dtype=dtype, device=self.device) if grp.need.values else grp.k
         state_tensors: dict[tuple[int, int], torch.Tensor | None] = {}
         for i, need in self._state_entries:
             # one slot more than there are requests: the padding rows of a captured graph read and write it
@@ -204,7 +204,7 @@ class CacheManager:
         return sum(g.bytes_per_token(item) for g in self.groups)
 
     def pool_bytes(self) -> int:
-        return sum(g.k.numel() * g.k.element_size() * 2 for g in self.groups if g.k is not None)
+        return sum(g.k.numel() * g.k.element_size() * (2 if g.need.values else 1) for g in self.groups if g.k is not None)
 
     def state_bytes(self) -> int:
         """Bytes of the per-request state tensors (one slot per request the cache can hold)."""

@@ -1,12 +1,13 @@
 from .presets import PRESETS, preset
 from .fekulix import FekulixConfig
+from .mugipel import MugipelConfig
 from .qwen3 import Qwen3Config
 from .registry import (Architecture, architecture_of, architectures, load_config_dict,
                        register_architecture, resolve, unregister_architecture)
 from .spec import LayerSpec, ModelSpec, PartSpec, RunEntry, TensorRule
 
 __all__ = [
-    "Architecture", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "TensorRule", "PRESETS", "FekulixConfig", "Qwen3Config",
+    "Architecture", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "TensorRule", "PRESETS", "FekulixConfig", "MugipelConfig", "Qwen3Config",
     "architecture_of", "architectures", "load_config_dict", "preset", "register_architecture",
     "resolve", "unregister_architecture",
 ]

@@ -52,10 +52,14 @@ class RunEntry:
     """One entry of the run order: run ``layer`` (an index into ``ModelSpec.layers``; the
     same layer may appear more than once and then shares its weights). Each entry has a
     cache of its own unless ``cache_of`` names an earlier entry whose cache it reads
-    instead of writing one."""
+    instead of writing one. ``transition``: an index into ``ModelSpec.transitions``; that part acts on the
+    residual stream right before this entry's layer, with ``transition_arg`` (for instance the number of
+    the pass that the entry opens)."""
 
     layer: int
     cache_of: int | None = None
+    transition: int | None = None
+    transition_arg: int = 0
 
 
 @dataclass(frozen=True)
@@ -90,9 +94,12 @@ class ModelSpec:
     head: PartSpec
     final_norm_prefix: str  # tensor-name prefix of the norm before the head (e.g. ``model.norm.``)
     checkpoint_rules: tuple[TensorRule, ...] = ()
+    transitions: tuple[PartSpec, ...] = ()  # parts of category ``transition`` that run entries may name
 
     def __post_init__(self):
         for i, e in enumerate(self.run_order):
+            if e.transition is not None and not 0 <= e.transition < len(self.transitions):
+                raise ValueError(f"run_order[{i}] names transition {e.transition}, the model has {len(self.transitions)}")
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"run_order[{i}] names layer {e.layer}, the model has {len(self.layers)}")
             if e.cache_of is not None and not 0 <= e.cache_of < i:

@@ -29,7 +29,8 @@ attention_rowwise_kernel(T* __restrict__ out,            // [T, nq, d]
                          const int* __restrict__ positions, const int* __restrict__ row_of_token,
                          const int* __restrict__ page_indptr, const int* __restrict__ page_indices,
                          int num_tokens, int nq, int nkv, int d, float scale, int window, int sink, int page_shift,
-                         int num_pages, int* __restrict__ status) {
+                         int num_pages, int* __restrict__ status, const float* __restrict__ sink_values, float softcap,
+                         int chunk) {
   extern __shared__ float q_smem[];  // [warps][d]
   pdl_prologue();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -41,7 +42,9 @@ attention_rowwise_kernel(T* __restrict__ out,            // [T, nq, d]
   const int row = row_of_token[t];
   const int* pages = page_indices + page_indptr[row];
   const int page_size = 1 << page_shift;
-  const int lo = window > 0 ? max(0, qpos - window + 1) : 0;
+  int lo = window > 0 ? max(0, qpos - window + 1) : 0;
+  if (chunk > 0) lo = max(lo, (qpos / chunk) * chunk);  // blocks of `chunk` positions counted from the sequence's start
+  const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
 
   float* qs = q_smem + warp * d;
   const T* qsrc = q + ((size_t)t * nq + h) * d;
@@ -72,6 +75,7 @@ attention_rowwise_kernel(T* __restrict__ out,            // [T, nq, d]
         float dot = 0.f;
         for (int c = 0; c < d; ++c) dot = fmaf(qs[c], Elem<T>::load(kr + c), dot);
         s = dot * scale;
+        if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
       }
     }
     const float m_tile = warp_max(s);
@@ -94,7 +98,16 @@ attention_rowwise_kernel(T* __restrict__ out,            // [T, nq, d]
     }
     m = m_new;
   }
-  if (sink) l += expf(-m);  // one more term of score 0 in the denominator, with no value
+  if (sink) {
+    // one more term in the denominator, with no value: of score 0, or of the head's own learned score
+    // (which is neither scaled nor squashed). A row that sees no key at all is then all sink: output 0.
+    const float s0 = sink_values ? sink_values[h] : 0.f;
+    const float m_all = fmaxf(m, s0);
+    const float a = (m == -INFINITY) ? 0.f : expf(m - m_all);
+    l = l * a + expf(s0 - m_all);
+#pragma unroll
+    for (int i = 0; i < ROWWISE_MAX_D / 32; ++i) acc[i] *= a;
+  }
   T* o = out + ((size_t)t * nq + h) * d;
 #pragma unroll
   for (int i = 0; i < ROWWISE_MAX_D / 32; ++i) {
@@ -110,8 +123,10 @@ using namespace ms;
 MS_EXPORT int ms_attention_rowwise(void* out, const void* q, const void* k_pool, const void* v_pool,
                                    const int* positions, const int* row_of_token, const int* page_indptr,
                                    const int* page_indices, int num_tokens, int nq, int nkv, int head_dim, float scale,
-                                   int window, int sink, int page_size, int num_pages, int* status, int dtype, cudaStream_t stream) {
+                                   int window, int sink, int page_size, int num_pages, int* status, int dtype, cudaStream_t stream,
+                                   const float* sink_values, float softcap, int chunk) {
   if (num_tokens == 0) return 0;
+  MS_CHECK_ARG(softcap >= 0.f && chunk >= 0, "attention: softcap=%g and chunk=%d must not be negative", softcap, chunk);
   MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
   MS_CHECK_ARG(head_dim > 0 && head_dim <= ROWWISE_MAX_D, "attention: head_dim=%d is outside 1..%d", head_dim, ROWWISE_MAX_D);
   MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "attention: page_size=%d must be a power of two", page_size);
@@ -124,11 +139,11 @@ MS_EXPORT int ms_attention_rowwise(void* out, const void* q, const void* k_pool,
   if (dtype == MS_F32)
     MS_LAUNCH(attention_rowwise_kernel<float>, blocks, warps * 32, smem, stream,
         (float*)out, (const float*)q, (const float*)k_pool, (const float*)v_pool, positions, row_of_token, page_indptr,
-        page_indices, num_tokens, nq, nkv, head_dim, scale, window, sink, page_shift, num_pages, status);
+        page_indices, num_tokens, nq, nkv, head_dim, scale, window, sink, page_shift, num_pages, status, sink_values, softcap, chunk);
   else
     MS_LAUNCH(attention_rowwise_kernel<__nv_bfloat16>, blocks, warps * 32, smem, stream,
         (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
         positions, row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, head_dim, scale, window, sink, page_shift,
-        num_pages, status);
+        num_pages, status, sink_values, softcap, chunk);
   return 0;
 }

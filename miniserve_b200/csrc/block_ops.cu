@@ -1,0 +1,363 @@
+// Pointwise kernels of layer arrangements and mixers beyond the pre-norm block:
+//
+//   * RMSNorm whose scale is `offset + w` with w kept in float32 (a weight stored as the distance from
+//     one), with the residual add fused in as in add_rmsnorm and the addend multiplied by a constant
+//     first: h = residual + s * delta; out = h / sqrt(mean(h^2) + eps) * (offset + w);
+//   * the input of a product that re-enters the stream: [residual + s * delta | table[token]] side by
+//     side in the run's dtype (the second half is the embedding of the token, the stream's first value);
+//   * a row vector added to every row of a float32 matrix;
+//   * relu(x)^2 written at a column offset of a wider row;
+//   * a sigmoid gate per (token, channel) on attention's output, cut to the value size and written at a
+//     column offset of a wider row;
+//   * the cos/sin table of a step with a factor on both (rotations whose frequencies were rescaled for
+//     longer contexts carry such a factor);
+//   * the latent of latent attention: a column range of a projection, RMS-normed with a float32
+//     weight, written into its page padded with zeros to the cache's head size.
+//
+// Statistics, gates, angles and the residual sum are float32; each output is rounded once.
+#include "common.cuh"
+
+namespace ms {
+
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+add_rmsnorm_scaled_kernel(T* __restrict__ out, float* __restrict__ residual, const T* __restrict__ delta, float delta_scale,
+                          const float* __restrict__ w, float w_offset, const int* __restrict__ rows, float eps, int hidden,
+                          int write_residual) {
+  extern __shared__ float row_buf[];  // hidden floats
+  __shared__ float red[32];
+  pdl_prologue();
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* res = residual + (size_t)r * hidden;
+  const T* dl = delta ? delta + (size_t)r * hidden : nullptr;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += THREADS) {
+    float h = res[c];
+    if (dl) h = fmaf(delta_scale, Elem<T>::load(dl + c), h);
+    row_buf[c] = h;
+    ss += h * h;
+  }
+  const float total = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+  T* o = out + (size_t)i * hidden;
+  for (int c = threadIdx.x; c < hidden; c += THREADS) {
+    const float h = row_buf[c];
+    if (write_residual && dl) res[c] = h;
+    Elem<T>::store(o + c, (h * inv) * (w_offset + w[c]));
+  }
+}
+
+// bfloat16 rows that are a multiple of 8 wide and at most 8 * THREADS: eight elements per thread, kept in registers
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+add_rmsnorm_scaled_bf16x8_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ residual,
+                                 const __nv_bfloat16* __restrict__ delta, float delta_scale, const float* __restrict__ w,
+                                 float w_offset, const int* __restrict__ rows, float eps, int hidden, int write_residual) {
+  __shared__ float red[32];
+  pdl_prologue();
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* res = residual + (size_t)r * hidden;
+  const __nv_bfloat16* dl = delta ? delta + (size_t)r * hidden : nullptr;
+  const int c = threadIdx.x;
+  const bool mine = c < (hidden >> 3);
+  float h[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  float ss = 0.f;
+  if (mine) {
+    const float4 a = *reinterpret_cast<const float4*>(res + 8 * c), b = *reinterpret_cast<const float4*>(res + 8 * c + 4);
+    h[0] = a.x; h[1] = a.y; h[2] = a.z; h[3] = a.w; h[4] = b.x; h[5] = b.y; h[6] = b.z; h[7] = b.w;
+    if (dl) {
+      float d[8];
+      bf16x8_to_float(*reinterpret_cast<const uint4*>(dl + 8 * c), d);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) h[e] = fmaf(delta_scale, d[e], h[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += h[e] * h[e];
+  }
+  const float total = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+  if (!mine) return;
+  if (write_residual && dl) {
+    *reinterpret_cast<float4*>(res + 8 * c) = make_float4(h[0], h[1], h[2], h[3]);
+    *reinterpret_cast<float4*>(res + 8 * c + 4) = make_float4(h[4], h[5], h[6], h[7]);
+  }
+  const float4 wa = *reinterpret_cast<const float4*>(w + 8 * c), wb = *reinterpret_cast<const float4*>(w + 8 * c + 4);
+  const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+  float y[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) y[e] = (h[e] * inv) * (w_offset + wv[e]);
+  *reinterpret_cast<uint4*>(out + (size_t)i * hidden + 8 * c) = float_to_bf16x8(y);
+}
+
+// out[t, 0:W] = residual[t] + s * delta[t];  out[t, W:2W] = table[ids[t]]   (out rows are 2W wide)
+template <typename T>
+__global__ void stream_concat_kernel(T* __restrict__ out, const float* __restrict__ residual, const T* __restrict__ delta,
+                                     float delta_scale, const T* __restrict__ table, const int* __restrict__ ids, int vocab,
+                                     int hidden, int write_first, int write_second) {
+  pdl_prologue();
+  const int t = blockIdx.x;
+  T* o = out + (size_t)t * 2 * hidden;
+  if (write_first) {
+    const float* res = residual + (size_t)t * hidden;
+    const T* dl = delta ? delta + (size_t)t * hidden : nullptr;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      float h = res[c];
+      if (dl) h = fmaf(delta_scale, Elem<T>::load(dl + c), h);
+      Elem<T>::store(o + c, h);
+    }
+  }
+  if (write_second) {
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    const T* src = table + (size_t)id * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[hidden + c] = src[c];
+  }
+}
+
+__global__ void add_row_vector_kernel(float* __restrict__ x, const float* __restrict__ vec, long long total, int width) {
+  pdl_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) x[i] += vec[(int)(i % width)];
+}
+
+template <typename T>
+__global__ void relu_squared_kernel(T* __restrict__ out, int ld_out, const T* __restrict__ x, int ld_x, long long total, int width) {
+  pdl_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / width;
+  const int c = (int)(i - t * width);
+  const float z = fmaxf(Elem<T>::load(x + t * ld_x + c), 0.f);
+  Elem<T>::store(out + t * ld_out + c, z * z);
+}
+
+__global__ void relu_squared_bf16x8_kernel(__nv_bfloat16* __restrict__ out, int ld_out, const __nv_bfloat16* __restrict__ x, int ld_x,
+                                           long long total8, int width8) {
+  pdl_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total8) return;
+  const long long t = i / width8;
+  const int c = (int)(i - t * width8);
+  float v[8];
+  bf16x8_to_float(*reinterpret_cast<const uint4*>(x + t * ld_x + 8 * c), v);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float z = fmaxf(v[e], 0.f);
+    v[e] = z * z;
+  }
+  *reinterpret_cast<uint4*>(out + t * ld_out + 8 * c) = float_to_bf16x8(v);
+}
+
+// out[t, h * dv + c] = scale * sigmoid(gate[t, h * dv + c]) * attn[t, h, c]   (c < dv; attn rows are D wide)
+template <typename T>
+__global__ void channel_gate_kernel(T* __restrict__ out, int ld_out, const T* __restrict__ attn, const T* __restrict__ gate,
+                                    int ld_gate, long long items, int nq, int d_pad, int dv, float scale) {
+  pdl_prologue();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= items) return;
+  const int c = (int)(idx % dv);
+  const long long th = idx / dv;
+  const int h = (int)(th % nq);
+  const long long t = th / nq;
+  const float g = scale / (1.0f + expf(-Elem<T>::load(gate + t * ld_gate + (size_t)h * dv + c)));
+  Elem<T>::store(out + t * ld_out + (size_t)h * dv + c, g * Elem<T>::load(attn + (t * nq + h) * d_pad + c));
+}
+
+__global__ void channel_gate_bf16x8_kernel(__nv_bfloat16* __restrict__ out, int ld_out, const __nv_bfloat16* __restrict__ attn,
+                                           const __nv_bfloat16* __restrict__ gate, int ld_gate, long long items8, int nq, int d_pad,
+                                           int dv8, float scale) {
+  pdl_prologue();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= items8) return;
+  const int c = (int)(idx % dv8);
+  const long long th = idx / dv8;
+  const int h = (int)(th % nq);
+  const long long t = th / nq;
+  float a[8], g[8];
+  bf16x8_to_float(*reinterpret_cast<const uint4*>(attn + (t * nq + h) * d_pad + 8 * c), a);
+  bf16x8_to_float(*reinterpret_cast<const uint4*>(gate + t * ld_gate + (size_t)h * dv8 * 8 + 8 * c), g);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) a[e] *= scale / (1.0f + expf(-g[e]));
+  *reinterpret_cast<uint4*>(out + t * ld_out + (size_t)h * dv8 * 8 + 8 * c) = float_to_bf16x8(a);
+}
+
+__global__ void rope_table_scaled_kernel(float* __restrict__ table, const int* __restrict__ positions,
+                                         const float* __restrict__ inv_freq, float factor, int num_tokens, int rot) {
+  pdl_prologue();
+  const int half = rot >> 1;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)num_tokens * half) return;
+  const int t = (int)(idx / half), j = (int)(idx - (long long)t * half);
+  float sn, cs;
+  sincosf((float)positions[t] * inv_freq[j], &sn, &cs);
+  table[(size_t)t * rot + j] = cs * factor;
+  table[(size_t)t * rot + half + j] = sn * factor;
+}
+
+// One warp per token: c = proj[t, off : off + rank] / rms * w, into the token's slot of its page.
+template <typename T>
+__global__ void latent_prepare_kernel(T* __restrict__ pool,  // [pages, 1, page_size, D]
+                                      const T* __restrict__ proj, int ld, int off, const float* __restrict__ w, float eps,
+                                      const int* __restrict__ positions, const int* __restrict__ row_of_token,
+                                      const int* __restrict__ page_indptr, const int* __restrict__ page_indices, int num_tokens,
+                                      int rank, int d_pad, int page_shift, int num_pages, int* __restrict__ status) {
+  pdl_prologue();
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= num_tokens) return;
+  const T* src = proj + (size_t)t * ld + off;
+  const int pos = positions[t], row = row_of_token[t];
+  const int page_size = 1 << page_shift;
+  const int page = page_indices[page_indptr[row] + (pos >> page_shift)];
+  if (page < 0) {
+    if (lane == 0) atomicExch(status, 2);
+    return;
+  }
+  MS_DEBUG_ONLY(if (page >= num_pages || row < 0) {
+    if (lane == 0) atomicExch(status, 5);
+    return;
+  })
+  T* dst = pool + ((size_t)page * page_size + (pos & (page_size - 1))) * d_pad;
+  float ss = 0.f;
+  for (int c = lane; c < rank; c += 32) {
+    const float x = Elem<T>::load(src + c);
+    ss += x * x;
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)rank + eps);
+  for (int c = lane; c < d_pad; c += 32) Elem<T>::store(dst + c, c < rank ? (Elem<T>::load(src + c) * inv) * w[c] : 0.f);
+}
+
+}  // namespace ms
+
+using namespace ms;
+
+MS_EXPORT int ms_add_rmsnorm_scaled(void* out, float* residual, const void* delta, float delta_scale, const float* w, float w_offset,
+                                    const int* rows, float eps, int n, int hidden, int write_residual, int dtype,
+                                    cudaStream_t stream) {
+  if (n == 0) return 0;
+  MS_CHECK_ARG(hidden > 0, "add_rmsnorm_scaled: hidden=%d", hidden);
+  const size_t smem = (size_t)hidden * sizeof(float);
+  if (dtype == MS_BF16 && hidden % 8 == 0 && hidden <= 8 * 1024 && (uintptr_t)out % 16 == 0 && (uintptr_t)residual % 16 == 0 &&
+      (uintptr_t)delta % 16 == 0 && (uintptr_t)w % 16 == 0) {
+    const int chunks = hidden / 8;
+    if (chunks <= 128)
+      MS_LAUNCH(add_rmsnorm_scaled_bf16x8_kernel<128>, n, 128, 0, stream, (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta,
+                delta_scale, w, w_offset, rows, eps, hidden, write_residual);
+    else if (chunks <= 256)
+      MS_LAUNCH(add_rmsnorm_scaled_bf16x8_kernel<256>, n, 256, 0, stream, (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta,
+                delta_scale, w, w_offset, rows, eps, hidden, write_residual);
+    else if (chunks <= 512)
+      MS_LAUNCH(add_rmsnorm_scaled_bf16x8_kernel<512>, n, 512, 0, stream, (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta,
+                delta_scale, w, w_offset, rows, eps, hidden, write_residual);
+    else
+      MS_LAUNCH(add_rmsnorm_scaled_bf16x8_kernel<1024>, n, 1024, 0, stream, (__nv_bfloat16*)out, residual, (const __nv_bfloat16*)delta,
+                delta_scale, w, w_offset, rows, eps, hidden, write_residual);
+    return 0;
+  }
+  MS_CHECK_ARG(smem <= 200 * 1024, "add_rmsnorm_scaled: a row of %d floats does not fit shared memory", hidden);
+  if (dtype == MS_F32) {
+    if (smem > 48 * 1024)
+      MS_CHECK_CUDA(cudaFuncSetAttribute(add_rmsnorm_scaled_kernel<float, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MS_LAUNCH((add_rmsnorm_scaled_kernel<float, 256>), n, 256, smem, stream, (float*)out, residual, (const float*)delta, delta_scale,
+              w, w_offset, rows, eps, hidden, write_residual);
+  } else {
+    if (smem > 48 * 1024)
+      MS_CHECK_CUDA(cudaFuncSetAttribute(add_rmsnorm_scaled_kernel<__nv_bfloat16, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem));
+    MS_LAUNCH((add_rmsnorm_scaled_kernel<__nv_bfloat16, 256>), n, 256, smem, stream, (__nv_bfloat16*)out, residual,
+              (const __nv_bfloat16*)delta, delta_scale, w, w_offset, rows, eps, hidden, write_residual);
+  }
+  return 0;
+}
+
+MS_EXPORT int ms_stream_concat(void* out, const float* residual, const void* delta, float delta_scale, const void* table,
+                               const int* ids, int vocab, int num_tokens, int hidden, int write_first, int write_second, int dtype,
+                               cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  MS_CHECK_ARG(hidden > 0 && vocab > 0, "stream_concat: hidden=%d vocab=%d", hidden, vocab);
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (dtype == MS_F32)
+    MS_LAUNCH(stream_concat_kernel<float>, num_tokens, threads, 0, stream, (float*)out, residual, (const float*)delta, delta_scale,
+              (const float*)table, ids, vocab, hidden, write_first, write_second);
+  else
+    MS_LAUNCH(stream_concat_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, (__nv_bfloat16*)out, residual,
+              (const __nv_bfloat16*)delta, delta_scale, (const __nv_bfloat16*)table, ids, vocab, hidden, write_first, write_second);
+  return 0;
+}
+
+MS_EXPORT int ms_add_row_vector(float* x, const float* vec, int rows, int width, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  const long long total = (long long)rows * width;
+  MS_LAUNCH(add_row_vector_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, x, vec, total, width);
+  return 0;
+}
+
+MS_EXPORT int ms_relu_squared(void* out, int ld_out, const void* x, int ld_x, int rows, int width, int dtype, cudaStream_t stream) {
+  if (rows == 0 || width == 0) return 0;
+  const long long total = (long long)rows * width;
+  if (dtype == MS_BF16 && width % 8 == 0 && ld_out % 8 == 0 && ld_x % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)x % 16 == 0) {
+    MS_LAUNCH(relu_squared_bf16x8_kernel, (unsigned)((total / 8 + 255) / 256), 256, 0, stream, (__nv_bfloat16*)out, ld_out,
+              (const __nv_bfloat16*)x, ld_x, total / 8, width / 8);
+    return 0;
+  }
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == MS_F32)
+    MS_LAUNCH(relu_squared_kernel<float>, blocks, 256, 0, stream, (float*)out, ld_out, (const float*)x, ld_x, total, width);
+  else
+    MS_LAUNCH(relu_squared_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, ld_out, (const __nv_bfloat16*)x, ld_x,
+              total, width);
+  return 0;
+}
+
+MS_EXPORT int ms_channel_gate(void* out, int ld_out, const void* attn, const void* gate, int ld_gate, int num_tokens, int nq, int d_pad,
+                              int dv, float scale, int dtype, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  MS_CHECK_ARG(nq > 0 && dv > 0 && dv <= d_pad && gate != nullptr, "channel_gate: bad sizes nq=%d dv=%d D=%d", nq, dv, d_pad);
+  const long long items = (long long)num_tokens * nq * dv;
+  if (dtype == MS_BF16 && dv % 8 == 0 && d_pad % 8 == 0 && ld_out % 8 == 0 && ld_gate % 8 == 0 && (uintptr_t)out % 16 == 0 &&
+      (uintptr_t)attn % 16 == 0 && (uintptr_t)gate % 16 == 0) {
+    MS_LAUNCH(channel_gate_bf16x8_kernel, (unsigned)((items / 8 + 255) / 256), 256, 0, stream, (__nv_bfloat16*)out, ld_out,
+              (const __nv_bfloat16*)attn, (const __nv_bfloat16*)gate, ld_gate, items / 8, nq, d_pad, dv / 8, scale);
+    return 0;
+  }
+  const unsigned blocks = (unsigned)((items + 255) / 256);
+  if (dtype == MS_F32)
+    MS_LAUNCH(channel_gate_kernel<float>, blocks, 256, 0, stream, (float*)out, ld_out, (const float*)attn, (const float*)gate, ld_gate,
+              items, nq, d_pad, dv, scale);
+  else
+    MS_LAUNCH(channel_gate_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, ld_out, (const __nv_bfloat16*)attn,
+              (const __nv_bfloat16*)gate, ld_gate, items, nq, d_pad, dv, scale);
+  return 0;
+}
+
+MS_EXPORT int ms_rope_table_scaled(float* table, const int* positions, const float* inv_freq, float factor, int num_tokens,
+                                   int rotary_dim, cudaStream_t stream) {
+  if (num_tokens == 0 || rotary_dim == 0) return 0;
+  MS_CHECK_ARG(rotary_dim > 0 && rotary_dim % 2 == 0, "rope_table_scaled: rotary_dim=%d must be even", rotary_dim);
+  const long long items = (long long)num_tokens * (rotary_dim / 2);
+  MS_LAUNCH(rope_table_scaled_kernel, (unsigned)((items + 255) / 256), 256, 0, stream, table, positions, inv_freq, factor, num_tokens,
+            rotary_dim);
+  return 0;
+}
+
+MS_EXPORT int ms_latent_prepare(void* pool, const void* proj, int ld, int off, const float* w, float eps, const int* positions,
+                                const int* row_of_token, const int* page_indptr, const int* page_indices, int num_tokens, int rank,
+                                int d_pad, int page_size, int num_pages, int* status, int dtype, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  MS_CHECK_ARG(rank > 0 && d_pad >= rank, "latent_prepare: bad sizes rank=%d D=%d", rank, d_pad);
+  MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "latent_prepare: page_size=%d must be a power of two", page_size);
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  const int warps = 4;
+  const unsigned blocks = (unsigned)((num_tokens + warps - 1) / warps);
+  if (dtype == MS_F32)
+    MS_LAUNCH(latent_prepare_kernel<float>, blocks, warps * 32, 0, stream, (float*)pool, (const float*)proj, ld, off, w, eps, positions,
+              row_of_token, page_indptr, page_indices, num_tokens, rank, d_pad, page_shift, num_pages, status);
+  else
+    MS_LAUNCH(latent_prepare_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream, (__nv_bfloat16*)pool, (const __nv_bfloat16*)proj, ld,
+              off, w, eps, positions, row_of_token, page_indptr, page_indices, num_tokens, rank, d_pad, page_shift, num_pages, status);
+  return 0;
+}

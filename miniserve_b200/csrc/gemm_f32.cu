@@ -11,7 +11,10 @@ constexpr int GBM = 64, GBN = 64, GBK = 16;
 
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(float* __restrict__ C, const float* __restrict__ A, const float* __restrict__ W, int M, int N, int K,
-                int lda, int ldw, int ldc) {
+                int lda, int ldw, int ldc, long long stride_a, long long stride_w, long long stride_c) {
+  A += blockIdx.z * stride_a;  // batches of independent products (per-head matrices): one z index each
+  W += blockIdx.z * stride_w;
+  C += blockIdx.z * stride_c;
   __shared__ float As[GBK][GBM + 4];
   __shared__ float Ws[GBK][GBN + 4];
   pdl_prologue();
@@ -73,6 +76,19 @@ MS_EXPORT int ms_gemm_f32(float* C, const float* A, const float* W, int M, int N
   MS_CHECK_ARG(lda >= K && ldw >= K && ldc >= N, "gemm_f32: leading dimensions too small");
   dim3 grid(ceil_div(N, GBN), ceil_div(M, GBM));
   MS_CHECK_ARG(grid.y <= 65535, "gemm_f32: M=%d too large for one launch", M);
-  MS_LAUNCH(gemm_f32_kernel, grid, 256, 0, stream, C, A, W, M, N, K, lda, ldw, ldc);
+  MS_LAUNCH(gemm_f32_kernel, grid, 256, 0, stream, C, A, W, M, N, K, lda, ldw, ldc, 0ll, 0ll, 0ll);
+  return 0;
+}
+
+// `batch` products of the same sizes: product b reads A + b * stride_a and W + b * stride_w and writes C + b * stride_c
+// (strides in elements; rows of different products may interleave, as heads do in a [tokens, heads, d] tensor).
+MS_EXPORT int ms_gemm_f32_batched(float* C, const float* A, const float* W, int M, int N, int K, int lda, int ldw, int ldc, int batch,
+                                  long long stride_a, long long stride_w, long long stride_c, cudaStream_t stream) {
+  if (M == 0 || N == 0 || batch == 0) return 0;
+  MS_CHECK_ARG(M > 0 && N > 0 && K > 0 && batch > 0 && batch <= 65535, "gemm_f32_batched: bad sizes M=%d N=%d K=%d batch=%d", M, N, K, batch);
+  MS_CHECK_ARG(lda >= K && ldw >= K && ldc >= N, "gemm_f32_batched: leading dimensions too small");
+  dim3 grid(ceil_div(N, GBN), ceil_div(M, GBM), batch);
+  MS_CHECK_ARG(grid.y <= 65535, "gemm_f32_batched: M=%d too large for one launch", M);
+  MS_LAUNCH(gemm_f32_kernel, grid, 256, 0, stream, C, A, W, M, N, K, lda, ldw, ldc, stride_a, stride_w, stride_c);
   return 0;
 }

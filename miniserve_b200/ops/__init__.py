@@ -8,12 +8,14 @@ product, which may go to the vendor library where the reference's engine does th
 from __future__ import annotations
 
 import ctypes
+from dataclasses import dataclass
 
 import torch
 
 from . import blas, native
-from .mixers import (add_dyt, axpby, conv_silu_unit, conv_state_update, decay_scan, gelu_tanh, head_gate,  # noqa: F401
-                     head_norm_gate, qkv_prepare, scale_)
+from .mixers import (add_dyt, add_rmsnorm_scaled, add_row_vector, axpby, channel_gate, conv_silu_unit,  # noqa: F401
+                     conv_state_update, decay_scan, gelu_tanh, head_gate, head_norm_gate, latent_prepare, qkv_prepare,
+                     relu_squared, rope_table_scaled, scale_, stream_concat)
 from .native import NativeError, OutOfBlocks
 
 __all__ = [
@@ -297,6 +299,25 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = Non
     return out
 
 
+def linear_heads(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, stream=None) -> torch.Tensor:
+    """out[t, h, :] = weight[h] x[t, h, :]: every head has a matrix of its own. x [T, H, K] and out [T, H, N] may be
+    views whose rows are part of wider ones; weight [H, N, K]. float32: this package's FFMA kernel, one launch over
+    all heads; bfloat16: the vendor library's strided batched product (float32 accumulation)."""
+    t, h, kdim = x.shape
+    n = weight.shape[1]
+    assert weight.shape == (h, n, kdim) and weight.is_contiguous() and out.shape == (t, h, n) and x.is_cuda
+    assert x.stride(2) == 1 and out.stride(2) == 1 and x.dtype == weight.dtype == out.dtype
+    if t == 0:
+        return out
+    if x.dtype == torch.float32:
+        native.kernel_check(native.kernels().ms_gemm_f32_batched(
+            _ptr(out), _ptr(x), _ptr(weight), t, n, kdim, x.stride(0), kdim, out.stride(0), h, x.stride(1), n * kdim, out.stride(1),
+            _stream(stream)))
+        return out
+    blas.gemm_bf16_batched(out, x, weight, _stream(stream))
+    return out
+
+
 def linear_gelu_tanh(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, stream=None) -> torch.Tensor:
     """out [M, N] = gelu_tanh(x W^T). bfloat16 with at most 16 rows where the weight-streaming kernel is
     the choice for the plain product: one kernel with the activation in its epilogue (the product is
@@ -430,21 +451,43 @@ def rope_table_tiled(table: torch.Tensor, stream=None) -> torch.Tensor:
     return tiled
 
 
+@dataclass(frozen=True)
+class AttentionExtras:
+    """What an attention may have beyond scale, window and a sink of score 0. ``sink_values``: float32 [heads], the
+    score of each head's sink (the denominator's extra term is exp(sink_h); it is neither scaled nor squashed).
+    ``softcap``: scores become softcap * tanh(score / softcap) after the scale. ``chunk``: a query at position p sees
+    only keys from floor(p / chunk) * chunk on, blocks being counted from position 0 of the sequence."""
+
+    sink_values: torch.Tensor | None = None
+    softcap: float = 0.0
+    chunk: int = 0
+
+    @property
+    def any(self) -> bool:
+        return self.sink_values is not None or bool(self.softcap) or bool(self.chunk)
+
+
+NO_EXTRAS = AttentionExtras()
+
+
 def attention_rowwise(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                       positions: torch.Tensor, row_of_token: torch.Tensor, page_indptr: torch.Tensor,
                       page_indices: torch.Tensor, scale: float, window: int | None, status: torch.Tensor,
-                      stream=None, sink: bool = False) -> None:
+                      stream=None, sink: bool = False, extras: "AttentionExtras | None" = None) -> None:
     """Causal attention of every new token over its request's pages; one warp per (token, head),
     float32 arithmetic in a fixed order (bit-identical however the tokens were batched)."""
     _check_dev(out, q, k_pool, v_pool, positions, row_of_token, page_indptr, page_indices, status)
+    extras = extras or NO_EXTRAS
+    assert extras.sink_values is None or (extras.sink_values.dtype == torch.float32 and extras.sink_values.numel() == q.shape[1])
     t, nq, d = q.shape
     nkv, page_size = k_pool.shape[1], k_pool.shape[2]
     assert out.shape == q.shape and k_pool.shape[3] == d and k_pool.dtype == q.dtype
     k = native.kernels()
     native.kernel_check(k.ms_attention_rowwise(
         _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(positions), _ptr(row_of_token), _ptr(page_indptr),
-        _ptr(page_indices), t, nq, nkv, d, float(scale), int(window or 0), int(sink), page_size, k_pool.shape[0], _ptr(status),
-        dtype_code(q.dtype), _stream(stream)))
+        _ptr(page_indices), t, nq, nkv, d, float(scale), int(window or 0), int(sink or extras.sink_values is not None), page_size,
+        k_pool.shape[0], _ptr(status), dtype_code(q.dtype), _stream(stream), _ptr(extras.sink_values), float(extras.softcap or 0.0),
+        int(extras.chunk or 0)))
 
 
 def nucleus_bytes() -> int:
@@ -475,14 +518,20 @@ def sample(tokens: torch.Tensor, logits: torch.Tensor, temperature: torch.Tensor
 
 
 def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
-              scale: float, window: int | None, sink: bool = False) -> None:
+              scale: float, window: int | None, sink: bool = False, extras: AttentionExtras | None = None) -> None:
     """Causal attention of the step's new tokens over the paged cache of cache group ``group``.
     ``sink``: one more term of score 0 in the softmax's denominator, which carries no value.
+    ``extras``: learned sink scores, a cap on the scores, a mask by blocks of positions (``AttentionExtras``).
 
     float32 runs the row-wise kernel (bit-identical however the step was cut). bfloat16 runs the
     tensor-core kernels when they take this head size, else the row-wise kernel too."""
     from . import attention_bf16
 
+    extras = extras if extras is not None and extras.any else None
+    if extras is not None and not (q.dtype == torch.bfloat16 and attention_bf16.takes_extras(q.shape[2], k_pool.shape[2])):
+        attention_rowwise(out, q, k_pool, v_pool, ctx.positions, ctx.row_of_token, ctx.page_indptr[group],
+                          ctx.page_indices[group], scale, window, ctx.status, stream=ctx.stream, sink=sink, extras=extras)
+        return
     recorder = getattr(ctx, "recorder", None)
     if recorder is not None and q.dtype == torch.bfloat16 and (attention_tc_ok(q, k_pool) or attention_bf16.supports(q.shape[2], k_pool.shape[2])):
         # The pass is being captured into CUDA graphs. Which tensor-core kernels run here, their grids and

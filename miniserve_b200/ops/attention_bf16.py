@@ -27,6 +27,11 @@ def supports(head_dim: int, page_size: int) -> bool:
     return head_dim % 16 == 0 and 16 <= head_dim <= 256 and page_size & (page_size - 1) == 0
 
 
+def takes_extras(head_dim: int, page_size: int) -> bool:
+    """Whether these kernels take learned sink scores, a cap on the scores and a mask by blocks of positions."""
+    return False
+
+
 def module_for(head_dim: int) -> build.Module:
     return build.Module(f"attn_bf16_d{head_dim}", ("attention_bf16.cu",), defines=(f"MS_HEAD_DIM={head_dim}",))
 

@@ -207,3 +207,31 @@ def gemm_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, stream: 
     _check(lib.cublasGemmEx(handle, _OP_T, _OP_N, n, m, k, _p_one, weight.data_ptr(), _R_16BF, k, x.data_ptr(), _R_16BF, k,
                             _p_zero, out.data_ptr(), _R_32F if out.dtype == torch.float32 else _R_16BF, n, _COMPUTE_32F,
                             _GEMM_DEFAULT), "cublasGemmEx")
+
+
+def gemm_bf16_batched(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, stream: int) -> None:
+    """out[:, b, :] = x[:, b, :] times weight[b]^T for every b: ``batch`` independent products in one call
+    (``cublasGemmStridedBatchedEx``, bfloat16 operands, float32 accumulation). x [M, B, K] and out [M, B, N] may be
+    views whose rows are part of wider ones (last stride 1); weight [B, N, K] is contiguous. These are the
+    per-head matrices of a mixer whose heads each have a small matrix of their own."""
+    m, b, k = x.shape
+    n = weight.shape[1]
+    assert weight.shape == (b, n, k) and weight.is_contiguous() and out.shape == (m, b, n)
+    assert x.stride(2) == 1 and out.stride(2) == 1 and x.dtype == weight.dtype == out.dtype == torch.bfloat16
+    lib = _library()
+    if not hasattr(lib, "_ms_batched_declared"):
+        ll = ctypes.c_longlong
+        lib.cublasGemmStridedBatchedEx.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, ll,
+                                                   c_void_p, c_int, c_int, ll, c_void_p, c_void_p, c_int, c_int, ll, c_int, c_int, c_int]
+        lib.cublasGemmStridedBatchedEx.restype = c_int
+        lib._ms_batched_declared = True
+    entry = _handle(x.device)
+    handle = entry[0]
+    if entry[2] != stream:
+        _check(lib.cublasSetStream_v2(handle, stream), "cublasSetStream")
+        _check(lib.cublasSetWorkspace_v2(handle, entry[1].data_ptr(), _WORKSPACE_BYTES), "cublasSetWorkspace")
+        entry[2] = stream
+    # column-major view per product: out_b^T [N, M] = weight_b (as [K, N], transposed) times x_b^T [K, M]
+    _check(lib.cublasGemmStridedBatchedEx(
+        handle, _OP_T, _OP_N, n, m, k, _p_one, weight.data_ptr(), _R_16BF, k, n * k, x.data_ptr(), _R_16BF, x.stride(0), x.stride(1),
+        _p_zero, out.data_ptr(), _R_16BF, out.stride(0), out.stride(1), b, _COMPUTE_32F, _GEMM_DEFAULT), "cublasGemmStridedBatchedEx")

@@ -62,7 +62,7 @@ PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 80, 128, 256)
 
 # kernels of mixers, norms and feed-forwards that Qwen3 does not have (Dynamic Tanh, tanh-GELU, the general q|k|v step, gates,
 # the linear-attention recurrences): compiled when a model first needs one of them
-MIXERS = Module("mixers", ("mixer_pointwise.cu", "recurrence.cu"))
+MIXERS = Module("mixers", ("mixer_pointwise.cu", "block_ops.cu", "recurrence.cu"))
 GEMM_TC = Module("gemm_tc", ("gemm_tc.cu",))
 ATTN_TC = Module("attn_tc", ("attention_tc.cu",))
 

@@ -208,3 +208,79 @@ def head_norm_gate(out, o, weight, gate, eps: float, scale: float, gate_kind: st
     native.mixers_check(native.mixers().ms_head_norm_gate(
         _ptr(out), _rows(out), _ptr(o), _ptr(weight), _ptr(gate), _rows(gate), t, heads, dv, float(eps), float(scale),
         GATE_KINDS[gate_kind], _dt(out.dtype), _stream(stream)))
+
+
+# ---------------------------------------------------------------- csrc/block_ops.cu
+
+def add_rmsnorm_scaled(out, residual, delta, delta_scale: float, weight, weight_offset: float, eps: float, rows=None, num_rows=None,
+                       write_residual=True, stream=None) -> None:
+    """out[i] = h / sqrt(mean(h^2) + eps) * (weight_offset + weight) with h = residual[r] + delta_scale * delta[r],
+    r = rows[i] (or i); h is written back to ``residual`` when there is no gather. float32 arithmetic, float32 weight."""
+    _f32(residual, weight)
+    hidden = residual.shape[-1]
+    n = out.shape[0] if num_rows is None else num_rows
+    assert out.is_contiguous() and out.shape[-1] == hidden and weight.numel() == hidden
+    assert delta is None or (delta.dtype == out.dtype and delta.is_contiguous())
+    native.mixers_check(native.mixers().ms_add_rmsnorm_scaled(
+        _ptr(out), _ptr(residual), _ptr(delta), float(delta_scale), _ptr(weight), float(weight_offset), _ptr(rows), float(eps), n,
+        hidden, int(write_residual and rows is None), _dt(out.dtype), _stream(stream)))
+
+
+def stream_concat(out, residual, delta, delta_scale: float, table, ids, first: bool = True, second: bool = True, stream=None) -> None:
+    """out [T, 2W] in the run's dtype: columns 0..W-1 = residual + delta_scale * delta (float32 sum, rounded once),
+    columns W..2W-1 = table[ids] (``first`` / ``second``: which half to write)."""
+    _f32(residual)
+    t, w = residual.shape
+    assert out.is_contiguous() and out.shape == (t, 2 * w) and table.dtype == out.dtype and table.shape[1] == w and table.is_contiguous()
+    assert delta is None or (delta.dtype == out.dtype and delta.is_contiguous() and delta.shape == (t, w))
+    assert ids.dtype == torch.int32 and ids.numel() >= t
+    native.mixers_check(native.mixers().ms_stream_concat(
+        _ptr(out), _ptr(residual), _ptr(delta), float(delta_scale), _ptr(table), _ptr(ids), table.shape[0], t, w, int(first),
+        int(second), _dt(out.dtype), _stream(stream)))
+
+
+def add_row_vector(x: torch.Tensor, vec: torch.Tensor, stream=None) -> None:
+    """x [T, W] += vec [W], float32, in place."""
+    _f32(x, vec)
+    assert x.dim() == 2 and vec.numel() == x.shape[1]
+    native.mixers_check(native.mixers().ms_add_row_vector(_ptr(x), _ptr(vec), x.shape[0], x.shape[1], _stream(stream)))
+
+
+def relu_squared(out: torch.Tensor, x: torch.Tensor, stream=None) -> None:
+    """out = max(x, 0)^2, in float32, rounded once; both 2-d views whose rows may be part of wider ones (may be in place)."""
+    assert out.shape == x.shape and out.dtype == x.dtype
+    native.mixers_check(native.mixers().ms_relu_squared(_ptr(out), _rows(out), _ptr(x), _rows(x), x.shape[0], x.shape[1],
+                                                         _dt(x.dtype), _stream(stream)))
+
+
+def channel_gate(out: torch.Tensor, attn: torch.Tensor, gate: torch.Tensor, value_dim: int, scale: float = 1.0, stream=None) -> None:
+    """out[t, h * dv + c] = scale * sigmoid(gate[t, h * dv + c]) * attn[t, h, c] for c < dv; ``attn`` [T, heads, D],
+    ``out`` and ``gate`` 2-d views of wider rows."""
+    t, nq, d = attn.shape
+    assert attn.is_contiguous() and out.shape == (t, nq * value_dim) and out.dtype == attn.dtype
+    assert gate.shape == (t, nq * value_dim) and gate.dtype == attn.dtype
+    native.mixers_check(native.mixers().ms_channel_gate(
+        _ptr(out), _rows(out), _ptr(attn), _ptr(gate), _rows(gate), t, nq, d, value_dim, float(scale), _dt(attn.dtype), _stream(stream)))
+
+
+def rope_table_scaled(positions: torch.Tensor, inv_freq: torch.Tensor, factor: float, num_tokens: int, rotary_dim: int,
+                      stream=None) -> torch.Tensor:
+    """float32 [T, rotary_dim]: factor * cos, then factor * sin, of position * inv_freq for every token of a step."""
+    _f32(inv_freq)
+    table = torch.empty((num_tokens, rotary_dim), dtype=torch.float32, device=inv_freq.device)
+    native.mixers_check(native.mixers().ms_rope_table_scaled(_ptr(table), _ptr(positions), _ptr(inv_freq), float(factor), num_tokens,
+                                                              rotary_dim, _stream(stream)))
+    return table
+
+
+def latent_prepare(pool, latent, weight, eps: float, positions, row_of_token, page_indptr, page_indices, page_size: int, status,
+                   stream=None) -> None:
+    """``latent`` [T, R] (a view into a projection's rows) over its root mean square, times the float32 ``weight`` [R],
+    into each token's slot of ``pool`` [pages, 1, page_size, D], zero from R on."""
+    _f32(weight)
+    t, rank = latent.shape
+    assert pool.dim() == 4 and pool.shape[1] == 1 and pool.shape[2] == page_size and pool.shape[3] >= rank and pool.dtype == latent.dtype
+    assert weight.numel() == rank
+    native.mixers_check(native.mixers().ms_latent_prepare(
+        _ptr(pool), _ptr(latent), _rows(latent), 0, _ptr(weight), float(eps), _ptr(positions), _ptr(row_of_token), _ptr(page_indptr),
+        _ptr(page_indices), t, rank, pool.shape[3], page_size, pool.shape[0], _ptr(status), _dt(latent.dtype), _stream(stream)))

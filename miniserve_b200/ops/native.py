@@ -108,8 +108,9 @@ def kernels():
     _declare(lib, "ms_rope_table", [_p, _p, _p, _i, _i, _p])
     _declare(lib, "ms_rope_table_tile", [_p, _p, _i, _p])
     _declare(lib, "ms_gemm_f32", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_gemm_f32_batched", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _p])
     _declare(lib, "ms_attention_rowwise",
-             [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p, _i, _p])
+             [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p, _i, _p, _p, _f, _i])
     _declare(lib, "ms_nucleus_bytes", [])
     _declare(lib, "ms_sample_scratch_bytes", [_i, _i], _ll)
     _declare(lib, "ms_sample", [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p])
@@ -136,6 +137,13 @@ def mixers():
     _declare(lib, "ms_conv_silu_unit", [_p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p])
     _declare(lib, "ms_conv_state_update", [_p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p])
     _declare(lib, "ms_head_norm_gate", [_p, _i, _p, _p, _p, _i, _i, _i, _i, _f, _f, _i, _i, _p])
+    _declare(lib, "ms_add_rmsnorm_scaled", [_p, _p, _p, _f, _p, _f, _p, _f, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_stream_concat", [_p, _p, _p, _f, _p, _p, _i, _i, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_add_row_vector", [_p, _p, _i, _i, _p])
+    _declare(lib, "ms_relu_squared", [_p, _i, _p, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_channel_gate", [_p, _i, _p, _p, _i, _i, _i, _i, _i, _f, _i, _p])
+    _declare(lib, "ms_rope_table_scaled", [_p, _p, _p, _f, _i, _i, _p])
+    _declare(lib, "ms_latent_prepare", [_p, _p, _i, _i, _p, _f, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _p])
     return lib
 
 

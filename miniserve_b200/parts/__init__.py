@@ -1,4 +1,4 @@
-from . import attention, block, embedding, linear_attention, mlp, norm, parallel, rope  # noqa: F401  (register the built-in parts)
+from . import attention, block, embedding, latent_attention, linear_attention, mlp, norm, parallel, rope, transition  # noqa: F401  (register the built-in parts)
 from .base import (BuildEnv, CacheNeed, FixedState, PagedKV, Part, ResidualStream, WeightDecl, build_part,
                    register_part, unregister_part)
 from .decoder import DecoderModel, EntryCache

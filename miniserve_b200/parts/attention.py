@@ -30,10 +30,17 @@ class GQAttention(Part):
     take the general kernels: one product makes q|k|v|gate, ``ops.qkv_prepare`` norms and rotates in
     float32 and writes keys and values padded with zeros to one cache head size (a zero channel changes
     no score and no output), and ``ops.head_gate`` cuts, gates and scales attention's output.
-    ``features`` stops before the output projection, for a mixer that joins several branches in one."""
+    ``features`` stops before the output projection, for a mixer that joins several branches in one.
+
+    More optional parameters: ``sink`` = ``"learned"`` (the sink's score is a tensor [heads], kept in float32, one
+    number per head, neither scaled nor capped), ``softcap`` (scores become softcap * tanh(score / softcap) after
+    the scale), ``chunk`` (a query at position p sees only keys from floor(p / chunk) * chunk on, blocks counted
+    from position 0 of the sequence; the cache then gives back pages that lie a whole block behind), and
+    ``out_gate`` = ``channel_sigmoid`` (attention's output is multiplied element by element by sigmoid(W_g x),
+    W_g as wide as the concatenated heads). All of them take the general path."""
     shape_static = True
     NAMES = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight", q_norm="q_norm.weight",
-                 k_norm="k_norm.weight", gate="g_proj.weight")
+                 k_norm="k_norm.weight", gate="g_proj.weight", sink="sink")
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -55,18 +62,30 @@ class GQAttention(Part):
         pos_spec = spec.get("position") or PartSpec("none")
         self.position = build_part("position", pos_spec, env)
         self.sink = bool(spec.get("sink", False))
+        self.learned_sink = spec.get("sink") == "learned"
+        self.softcap = float(spec.get("softcap") or 0.0)
+        self.chunk = int(spec.get("chunk") or 0)
+        if self.softcap < 0 or self.chunk < 0:
+            raise ValueError(f"softcap={self.softcap} and chunk={self.chunk} must not be negative")
         self.value_dim = int(spec.get("value_dim") or self.head_dim)
         self.out_gate = spec.get("out_gate")
-        if self.out_gate not in (None, "head_sigmoid"):
-            raise ValueError(f"out_gate must be 'head_sigmoid' or absent, got {self.out_gate!r}")
+        if self.out_gate not in (None, "head_sigmoid", "channel_sigmoid"):
+            raise ValueError(f"out_gate must be 'head_sigmoid', 'channel_sigmoid' or absent, got {self.out_gate!r}")
         self.names = {**self.NAMES, **dict(spec.get("names") or {})}
         self.adjacent = getattr(self.position, "pairing", "halves") == "adjacent"  # how the position encoding pairs channels
-        self.general = bool(self.out_gate or self.value_dim != self.head_dim or self.adjacent)
+        self.general = bool(self.out_gate or self.value_dim != self.head_dim or self.adjacent or self.learned_sink or self.softcap
+                            or self.chunk or getattr(self.position, "table_only", False))
+        self.w_sink = None
+        self.extras = None
         if self.general and not self.owns_cache:
             raise ValueError("a gate, a value size of its own or adjacent rotation pairs need a cache of the mixer's own")
         # the general path keeps keys and values in one head size: the larger of the two, in steps of 16
         self.cache_dim = -(-max(self.head_dim, self.value_dim) // 16) * 16 if self.general else self.head_dim
         self.feature_width = self.heads * self.value_dim
+
+    @property
+    def gate_width(self) -> int:
+        return self.heads * self.value_dim if self.out_gate == "channel_sigmoid" else (self.heads if self.out_gate else 0)
 
     @property
     def owns_cache(self) -> bool:
@@ -75,7 +94,9 @@ class GQAttention(Part):
     def cache_need(self):
         if not self.owns_cache:
             return None
-        return PagedKV(self.kv_heads, self.cache_dim, int(self.window) if self.window else None)
+        # keys a whole block behind the newest token are never seen again: the cache treats the block as a window
+        reach = min(int(self.window), self.chunk) if self.window and self.chunk else (int(self.window) if self.window else self.chunk)
+        return PagedKV(self.kv_heads, self.cache_dim, reach or None)
 
     def weights(self):
         d, n = self.head_dim, self.names
@@ -85,7 +106,9 @@ class GQAttention(Part):
             w[n["k"]] = WeightDecl((self.kv_heads * d, self.hidden))
             w[n["v"]] = WeightDecl((self.kv_heads * self.value_dim, self.hidden))
         if self.out_gate:
-            w[n["gate"]] = WeightDecl((self.heads, self.hidden))
+            w[n["gate"]] = WeightDecl((self.gate_width, self.hidden))
+        if self.learned_sink:
+            w[n["sink"]] = WeightDecl((self.heads,), precision="float32")
         if self.qk_norm:
             # the general kernel takes the norm's weights in float32, the others in the run's dtype
             kind = dict(precision="float32") if self.general else {}
@@ -115,6 +138,16 @@ class GQAttention(Part):
         self.w_o = tensors[n["o"]].contiguous()
         self.w_q_norm = tensors[n["q_norm"]].contiguous() if self.qk_norm else None
         self.w_k_norm = tensors[n["k_norm"]].contiguous() if self.qk_norm and self.owns_cache else None
+        self.w_sink = tensors[n["sink"]].float().contiguous() if self.learned_sink else None
+        if self.learned_sink or self.softcap or self.chunk:
+            self.extras = ops.AttentionExtras(self.w_sink, self.softcap, self.chunk)
+
+    @property
+    def reach(self) -> int | None:
+        """How far back the cache keeps keys for this mixer (what the kernels take as their window): the window, or the
+        block of a mask by blocks (which then does the masking itself, inside that reach)."""
+        need = self.cache_need()
+        return need.window if need is not None else (int(self.window) if self.window else None)
 
     def features(self, x: torch.Tensor, ctx, cache, out: torch.Tensor, scale: float = 1.0) -> None:
         """The general path up to the output projection's input: ``out`` [T, heads * value_dim] (a view
@@ -131,7 +164,10 @@ class GQAttention(Part):
                         ctx.positions, ctx.row_of_token, ctx.page_indptr[cache.group], ctx.page_indices[cache.group],
                         cache.page_size, ctx.status, stream=ctx.stream)
         att = ctx.buffer("attn.out", (t, nq, dc), dt, dev)
-        ops.attention(att, q, cache.k, cache.v, ctx, cache.group, self.scale, self.window, self.sink)
+        ops.attention(att, q, cache.k, cache.v, ctx, cache.group, self.scale, self.reach, self.sink, extras=self.extras)
+        if self.out_gate == "channel_sigmoid":
+            ops.channel_gate(out, att, proj[:, at_g:at_g + nq * dv], dv, scale, stream=ctx.stream)
+            return
         gate = proj[:, at_g:at_g + nq] if self.out_gate else None
         ops.head_gate(out, att, gate, dv, scale, stream=ctx.stream)
 

@@ -8,7 +8,7 @@ checkpoint tensors it wants by name relative to its own prefix, receives them in
 
 Categories and what each must provide:
 
-``norm``          ``forward(residual, delta, ctx, rows=None, write_residual=True) -> Tensor``
+``norm``          ``forward(residual, delta, ctx, rows=None, write_residual=True, delta_scale=1.0) -> Tensor``
 ``position``      ``kernel_table() -> (inv_freq | None, rotary_dim)``, ``step_table(ctx) -> cos/sin table | None``
 ``mixer``         ``cache_need() -> CacheNeed | tuple of them | None`` and ``forward(x, ctx, cache) -> Tensor``
                   (``cache``: the view of its need, or a tuple of views in the order of the needs)
@@ -16,6 +16,7 @@ Categories and what each must provide:
 ``block``         ``forward(stream, ctx, cache) -> ResidualStream`` (arranges the four above)
 ``embedding``     ``forward(ctx) -> float32 residual [T, hidden]``
 ``head``          ``forward(x, ctx) -> float32 logits [rows, vocab]``
+``transition``    ``forward(stream, ctx, embedding, arg) -> ResidualStream`` (acts on the stream between two layers)
 """
 
 from __future__ import annotations
@@ -27,7 +28,7 @@ import torch
 
 from ..config.spec import PartSpec
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head", "transition")
 _REGISTRY: dict[str, dict[str, type]] = {c: {} for c in CATEGORIES}
 
 
@@ -78,11 +79,14 @@ class WeightDecl:
 
 @dataclass(frozen=True)
 class PagedKV:
-    """A mixer's need for keys and values of every past token (or of the last ``window``)."""
+    """A mixer's need for keys and values of every past token (or of the last ``window``). ``values`` False: one
+    vector per token serves as key and as value (a latent that both are made from); the cache then keeps one pool
+    and hands it out as both."""
 
     kv_heads: int
     head_dim: int
     window: int | None = None
+    values: bool = True
 
 
 @dataclass(frozen=True)
@@ -168,10 +172,12 @@ class Part:
 class ResidualStream:
     """The residual stream between blocks: ``total`` (float32 [T, hidden]) plus an addend
     that has not been added yet (the last feed-forward output), so that the add can be
-    fused into the next norm."""
+    fused into the next norm. The addend counts ``pending_scale`` times (a block that adds its
+    sublayers' output times a constant hands the constant on instead of scaling the tensor)."""
 
     total: torch.Tensor
     pending: torch.Tensor | None = None
+    pending_scale: float = 1.0
 
 
 def param(spec: PartSpec, key: str, typ: type | None = None) -> Any:

@@ -2,8 +2,18 @@
 
 from __future__ import annotations
 
+import torch
+
+from .. import ops
 from ..config.spec import LayerSpec
 from .base import BuildEnv, Part, ResidualStream, build_part, register_part
+
+
+def _norm(norm, stream: ResidualStream, ctx):
+    """A block's first norm over the stream as the block before left it (its addend and the addend's factor)."""
+    if stream.pending_scale != 1.0:
+        return norm.forward(stream.total, stream.pending, ctx, delta_scale=stream.pending_scale)
+    return norm.forward(stream.total, stream.pending, ctx)
 
 
 @register_part("block", "prenorm")
@@ -35,13 +45,74 @@ class PreNormBlock(Part):
 
     def forward(self, stream: ResidualStream, ctx, cache) -> ResidualStream:
         total = stream.total
-        x = self.norm1.forward(total, stream.pending, ctx)
+        x = _norm(self.norm1, stream, ctx)
         a = self.mixer.forward(x, ctx, cache)
         if not self.has_ff:
             return ResidualStream(total, a)
         x = self.norm2.forward(total, a, ctx)
         return ResidualStream(total, self.feed_forward.forward(x, ctx))
 
+@register_part("block", "parallel_residual")
+class ParallelResidualBlock(Part):
+    """h = norm1(x); x += residual_mult * (mixer(h) + feed_forward(h)): one norm, both sublayers read its output.
+    When both can stop before their output projections (``features``, ``feature_width`` and ``w_o`` / ``w_down``),
+    they write their features side by side into one row and ONE product with the two output matrices joined along
+    their inputs makes the sum; otherwise the two outputs are added. The sum is handed on as the pending addend
+    with ``residual_mult`` as its factor, so the multiplication and the add happen in float32 inside the next norm.
+    Parameters: ``names`` (mixer / feed_forward / norm1 -> tensor-name prefixes), ``residual_mult``. A layer
+    without a feed-forward adds the mixer's output alone."""
+    shape_static = True
+
+    def __init__(self, spec, env: BuildEnv, layer: LayerSpec | None = None):
+        super().__init__(spec, env)
+        if layer is None:
+            raise ValueError("a block is built from its LayerSpec (use build_block)")
+        names = dict(spec.get("names") or {})
+        self.mult = float(spec.get("residual_mult", 1.0))
+        self.has_ff = layer.feed_forward is not None
+        self.names = {k: names[k] for k in ("mixer", "norm1") + (("feed_forward",) if self.has_ff else ())}
+        self.mixer = build_part("mixer", layer.mixer, env)
+        self.norm1 = build_part("norm", layer.norms["norm1"], env)
+        self.feed_forward = build_part("feed_forward", layer.feed_forward, env) if self.has_ff else None
+        self.joint = self.has_ff and all(hasattr(p, "features") and hasattr(p, "feature_width") for p in (self.mixer, self.feed_forward))
+        if self.joint and getattr(self.mixer, "general", True) is False:
+            self.joint = False  # an attention on its own fused path has no such stop
+        self.w_out = None
+
+    def sub_parts(self):
+        out = {self.names["mixer"]: self.mixer, self.names["norm1"]: self.norm1}
+        if self.has_ff:
+            out[self.names["feed_forward"]] = self.feed_forward
+        return out
+
+    def bind_all(self, tensors, prefix: str = "") -> None:
+        super().bind_all(tensors, prefix)
+        if self.joint:
+            w = torch.cat([self.mixer.w_o, self.feed_forward.w_down], dim=1)  # [hidden, mixer features + feed-forward features]
+            if w.shape[1] % 8:  # the product wants rows of whole 16 bytes: zero columns, which meet zero features
+                w = torch.cat((w, torch.zeros((w.shape[0], -w.shape[1] % 8), dtype=w.dtype, device=w.device)), dim=1)
+            self.w_out = w.contiguous()
+
+    def forward(self, stream: ResidualStream, ctx, cache) -> ResidualStream:
+        total = stream.total
+        x = _norm(self.norm1, stream, ctx)
+        if not self.has_ff:
+            return ResidualStream(total, self.mixer.forward(x, ctx, cache), self.mult)
+        t, dt, dev = x.shape[0], self.env.dtype, x.device
+        if self.joint:
+            fa, fb = self.mixer.feature_width, self.feed_forward.feature_width
+            feat = ctx.buffer("block.feat", (t, self.w_out.shape[1]), dt, dev)
+            self.mixer.features(x, ctx, cache, feat[:, :fa])
+            self.feed_forward.features(x, ctx, feat[:, fa:fa + fb])
+            if fa + fb < feat.shape[1]:
+                feat[:, fa + fb:].zero_()
+            y = ops.linear(feat, self.w_out, stream=ctx.stream, out=ctx.buffer("block.out", (t, self.w_out.shape[0]), dt, dev))
+            return ResidualStream(total, y, self.mult)
+        a = self.mixer.forward(x, ctx, cache)
+        b = self.feed_forward.forward(x, ctx)
+        y = ctx.buffer("block.out", tuple(a.shape), dt, dev)
+        ops.axpby(y, a, b, 1.0, 1.0, stream=ctx.stream)
+        return ResidualStream(total, y, self.mult)
 
 
 def build_block(layer: LayerSpec, env: BuildEnv) -> Part:

@@ -32,6 +32,7 @@ class DecoderModel:
         self.final_norm = build_part("norm", spec.final_norm, self.env)
         self.final_norm_name = spec.final_norm_prefix
         self.head = build_part("head", spec.head, self.env)
+        self.transitions = [build_part("transition", t, self.env) for t in spec.transitions]  # tensors by their full names
         self.entry_caches: list[EntryCache] = []
         for i, e in enumerate(spec.run_order):
             mixer = self.layers[e.layer].mixer
@@ -59,7 +60,7 @@ class DecoderModel:
                 subs.append(pos)
             return bool(getattr(part, "shape_static", False)) and all(ok(p) for p in subs)
 
-        return all(ok(p) for p in [self.embedding, self.final_norm, self.head, *self.layers])
+        return all(ok(p) for p in [self.embedding, self.final_norm, self.head, *self.layers, *self.transitions])
 
     @property
     def dtype(self) -> torch.dtype:
@@ -76,6 +77,8 @@ class DecoderModel:
             out.update(layer.all_weights(prefix))
         out.update(self.final_norm.all_weights(self.final_norm_name))
         out.update(self.head.all_weights())
+        for part in self.transitions:
+            out.update(part.all_weights())
         return out
 
     def weight_stacks(self) -> dict[str, tuple[str, ...]]:
@@ -91,6 +94,8 @@ class DecoderModel:
             layer.bind_all(tensors, prefix)
         self.final_norm.bind_all(tensors, self.final_norm_name)
         self.head.bind_all(tensors)
+        for part in self.transitions:
+            part.bind_all(tensors)
         if getattr(self.head, "tied", False):
             self.head.weight = self.embedding.table
         self.bound = True
@@ -118,6 +123,8 @@ class DecoderModel:
 
         for layer in self.layers:
             walk(layer)
+        for part in self.transitions:
+            walk(part)
         walk(self.final_norm)
         add(self.head.weight)
         return total
@@ -136,7 +143,10 @@ class DecoderModel:
         ctx.buffers.clear()
         stream = ResidualStream(self.embedding.forward(ctx))
         for i, entry in enumerate(self.spec.run_order):
+            if entry.transition is not None:
+                stream = self.transitions[entry.transition].forward(stream, ctx, self.embedding, entry.transition_arg)
             stream = self.layers[entry.layer].forward(stream, ctx, caches[i])
+        extra = {"delta_scale": stream.pending_scale} if stream.pending_scale != 1.0 else {}
         x = self.final_norm.forward(stream.total, stream.pending, ctx, rows=ctx.logit_rows,
-                                    num_rows=ctx.num_logit_rows, write_residual=False)
+                                    num_rows=ctx.num_logit_rows, write_residual=False, **extra)
         return self.head.forward(x, ctx)

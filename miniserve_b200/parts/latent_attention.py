@@ -1,0 +1,107 @@
+"""Attention whose keys and values are made from one small vector per token, the only thing cached."""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import PagedKV, Part, WeightDecl, param, register_part
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Part):
+    """q = W_q x; c = rmsnorm(W_down x) * w_norm, a vector of ``latent`` numbers per token; head h has keys
+    k_h = W_uk[h] c and values v_h = W_uv[h] c; causal softmax attention with scores (q_h . k_h) * scale, no
+    position encoding; the concatenated heads times sigmoid(W_g x) element by element; output projection.
+
+    Only c is cached, in pages of one "head" of size ``latent`` (rounded up to 16, zeros beyond) that serve as
+    keys and as values (``PagedKV(values=False)``). The per-head matrices are folded onto the query side:
+    q'_h = W_uk[h]^T q_h gives q_h . k_h = q'_h . c, so the framework's attention kernels run with every query
+    head reading the one cached vector (keys and values alike), and the value of head h is W_uv[h] applied to
+    attention's output over c. Two small products per head and step instead of keys and values of every head for
+    every cached token. The norm of c is float32; its weight stays float32.
+
+    Parameters: ``hidden``, ``heads``, ``head_dim``, ``value_dim``, ``latent``, ``scale``, ``eps``, ``names`` (q, down,
+    norm, up_k, up_v, gate, o -> tensor names). ``features`` stops before the output projection."""
+    shape_static = True
+    general = True
+    NAMES = dict(q="q_proj.weight", down="kv_down_proj.weight", norm="kv_norm.weight", up_k="k_up_proj.weight",
+                 up_v="v_up_proj.weight", gate="g_proj.weight", o="o_proj.weight")
+    MAX_LATENT = 256  # the largest head size the attention kernels take
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = param(spec, "hidden", int)
+        self.heads = param(spec, "heads", int)
+        self.head_dim = param(spec, "head_dim", int)
+        self.value_dim = param(spec, "value_dim", int)
+        self.latent = param(spec, "latent", int)
+        self.scale = float(spec.get("scale") or self.head_dim ** -0.5)
+        self.eps = param(spec, "eps", float)
+        self.names = {**self.NAMES, **dict(spec.get("names") or {})}
+        self.cache_dim = -(-self.latent // 16) * 16
+        if self.cache_dim > self.MAX_LATENT:
+            raise NotImplementedError(f"latent_attention: a latent of {self.latent} numbers is beyond the attention kernels' "
+                                      f"largest head size ({self.MAX_LATENT})")
+        self.feature_width = self.heads * self.value_dim
+
+    def cache_need(self):
+        return PagedKV(1, self.cache_dim, None, values=False)
+
+    def weights(self):
+        n, h = self.names, self.heads
+        return {n["q"]: WeightDecl((h * self.head_dim, self.hidden)),
+                n["down"]: WeightDecl((self.latent, self.hidden)),
+                n["norm"]: WeightDecl((self.latent,), precision="float32", init="ones_normal"),
+                n["up_k"]: WeightDecl((h * self.head_dim, self.latent)),
+                n["up_v"]: WeightDecl((h * self.value_dim, self.latent)),
+                n["gate"]: WeightDecl((h * self.value_dim, self.hidden)),
+                n["o"]: WeightDecl((self.hidden, h * self.value_dim))}
+
+    def _stack(self):
+        n = self.names
+        return "in_proj.weight", (n["q"], n["down"], n["gate"])
+
+    def stacks(self):
+        return dict([self._stack()])  # one product makes q, the latent before its norm, and the gate
+
+    def bind(self, tensors):
+        n, h, r, rc = self.names, self.heads, self.latent, self.cache_dim
+        w_in = self.joined(tensors, *self._stack())
+        if w_in.shape[0] % 8:  # rows of the product's output start on 16 bytes: a few zero rows at the end
+            w_in = torch.cat((w_in, torch.zeros((-w_in.shape[0] % 8, self.hidden), dtype=w_in.dtype, device=w_in.device)), dim=0)
+        self.w_in = w_in.contiguous()
+        self.w_norm = tensors[n["norm"]].float().contiguous()
+        uk = tensors[n["up_k"]].view(h, self.head_dim, r)
+        uv = tensors[n["up_v"]].view(h, self.value_dim, r)
+        # [heads, latent (padded), head_dim]: q' = W_uk[h]^T q; padded rows are zero, so q' is zero where the cache is
+        self.w_uk_t = torch.zeros((h, rc, self.head_dim), dtype=uk.dtype, device=uk.device)
+        self.w_uk_t[:, :r] = uk.transpose(1, 2)
+        # [heads, value_dim, latent (padded)]
+        self.w_uv = torch.zeros((h, self.value_dim, rc), dtype=uv.dtype, device=uv.device)
+        self.w_uv[:, :, :r] = uv
+        self.w_o = tensors[n["o"]].contiguous()
+
+    def features(self, x: torch.Tensor, ctx, cache, out: torch.Tensor, scale: float = 1.0) -> None:
+        """``out`` [T, heads * value_dim] (a view whose rows may be part of wider ones) = scale * gate * attention."""
+        t = x.shape[0]
+        dt, dev = self.env.dtype, self.w_in.device
+        h, dk, dv, r, rc = self.heads, self.head_dim, self.value_dim, self.latent, self.cache_dim
+        proj = ops.linear(x, self.w_in, stream=ctx.stream, out=ctx.buffer("lat.in", (t, self.w_in.shape[0]), dt, dev))
+        at_c, at_g = h * dk, h * dk + r
+        ops.latent_prepare(cache.k, proj[:, at_c:at_g], self.w_norm, self.eps, ctx.positions, ctx.row_of_token,
+                           ctx.page_indptr[cache.group], ctx.page_indices[cache.group], cache.page_size, ctx.status, stream=ctx.stream)
+        q = ctx.buffer("lat.q", (t, h, rc), dt, dev)
+        ops.linear_heads(proj[:, :at_c].unflatten(1, (h, dk)), self.w_uk_t, q, stream=ctx.stream)
+        att = ctx.buffer("lat.att", (t, h, rc), dt, dev)
+        ops.attention(att, q, cache.k, cache.v, ctx, cache.group, self.scale, None, False)
+        val = ctx.buffer("lat.val", (t, h, dv), dt, dev)
+        ops.linear_heads(att, self.w_uv, val, stream=ctx.stream)
+        ops.channel_gate(out, val, proj[:, at_g:at_g + h * dv], dv, scale, stream=ctx.stream)
+
+    def forward(self, x: torch.Tensor, ctx, cache):
+        t = x.shape[0]
+        dt, dev = self.env.dtype, self.w_in.device
+        feat = ctx.buffer("lat.feat", (t, self.feature_width), dt, dev)
+        self.features(x, ctx, cache, feat)
+        return ops.linear(feat, self.w_o, stream=ctx.stream, out=ctx.buffer("lat.proj", (t, self.w_o.shape[0]), dt, dev))

@@ -51,7 +51,9 @@ class SwiGLU(Part):
 @register_part("feed_forward", "dense_mlp")
 class DenseMLP(Part):
     """down(act(up(x))), no gate and no biases. Parameters: ``hidden``, ``intermediate``, ``activation``
-    (``gelu_tanh``: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))), ``names`` (up / down -> tensor names)."""
+    (``gelu_tanh``: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); ``relu_squared``: max(z, 0)^2), ``names``
+    (up / down -> tensor names). ``features`` stops before the down projection, for a block that joins it with
+    another part's output projection."""
     shape_static = True
 
     def __init__(self, spec, env):
@@ -59,8 +61,9 @@ class DenseMLP(Part):
         self.hidden = param(spec, "hidden", int)
         self.inter = param(spec, "intermediate", int)
         self.activation = spec.get("activation", "gelu_tanh")
-        if self.activation != "gelu_tanh":
-            raise ValueError(f"dense_mlp knows the activation 'gelu_tanh', not {self.activation!r}")
+        if self.activation not in ("gelu_tanh", "relu_squared"):
+            raise ValueError(f"dense_mlp knows the activations 'gelu_tanh' and 'relu_squared', not {self.activation!r}")
+        self.feature_width = self.inter
         names = dict(spec.get("names") or {})
         self.names = {"up": names.get("up", "up_proj.weight"), "down": names.get("down", "down_proj.weight")}
 
@@ -72,8 +75,22 @@ class DenseMLP(Part):
         self.w_up = tensors[self.names["up"]].contiguous()
         self.w_down = tensors[self.names["down"]].contiguous()
 
+    def features(self, x, ctx, out: torch.Tensor) -> None:
+        """``out`` [T, intermediate] (a view whose rows may be part of wider ones) = act(up(x))."""
+        t, dt, dev = x.shape[0], self.env.dtype, self.w_down.device
+        up = ops.linear(x, self.w_up, stream=ctx.stream, out=ctx.buffer("mlp.up", (t, self.inter), dt, dev))
+        if self.activation == "relu_squared":
+            ops.relu_squared(out, up, stream=ctx.stream)
+        else:
+            ops.gelu_tanh(up, up, stream=ctx.stream)
+            out.copy_(up)
+
     def forward(self, x, ctx) -> torch.Tensor:
         t, dt, dev = x.shape[0], self.env.dtype, self.w_down.device
+        if self.activation == "relu_squared":
+            act = ctx.buffer("mlp.act", (t, self.inter), dt, dev)
+            self.features(x, ctx, act)
+            return ops.linear(act, self.w_down, stream=ctx.stream, out=ctx.buffer("mlp.down", (t, self.hidden), dt, dev))
         # the activation in the product's epilogue where there is such a kernel (decode steps)
         act = ops.linear_gelu_tanh(x, self.w_up, ctx.buffer("mlp.act", (t, self.inter), dt, dev), stream=ctx.stream)
         return ops.linear(act, self.w_down, stream=ctx.stream, out=ctx.buffer("mlp.down", (t, self.hidden), dt, dev))

@@ -11,23 +11,41 @@ from .base import Part, WeightDecl, param, register_part
 @register_part("norm", "rmsnorm")
 class RMSNorm(Part):
     """y = x * rsqrt(mean(x^2) + eps) * weight, statistics in float32, no bias and no ``1 +``
-    offset (miniserve/model/qwen3.py:78-82). Parameters: ``size``, ``eps``."""
+    offset (miniserve/model/qwen3.py:78-82). Parameters: ``size``, ``eps``; optional ``unit_offset`` (the
+    stored weight is the scale's distance from one: y = x * rsqrt(mean(x^2) + eps) * (1 + weight); the weight
+    then stays float32 whatever the run's dtype, so that 1 + weight is not rounded) and ``name`` (the
+    tensor's name relative to the part's prefix, default ``weight``)."""
     shape_static = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.size = param(spec, "size", int)
         self.eps = param(spec, "eps", float)
+        self.unit_offset = bool(spec.get("unit_offset", False))
+        self.name = spec.get("name", "weight")
+        self._w_f32 = None
 
     def weights(self):
-        return {"weight": WeightDecl((self.size,), init="ones_normal")}
+        if self.unit_offset:
+            return {self.name: WeightDecl((self.size,), precision="float32")}
+        return {self.name: WeightDecl((self.size,), init="ones_normal")}
+
+    def bind(self, tensors):
+        self.w_weight = tensors[self.name].contiguous()
+        self._w_f32 = self.w_weight if self.w_weight.dtype == torch.float32 else None
 
     def forward(self, residual: torch.Tensor, delta: torch.Tensor | None, ctx, rows: torch.Tensor | None = None,
-                num_rows: int | None = None, write_residual: bool = True) -> torch.Tensor:
-        """Normalise ``residual (+ delta)``; without ``rows`` the sum is stored back into
+                num_rows: int | None = None, write_residual: bool = True, delta_scale: float = 1.0) -> torch.Tensor:
+        """Normalise ``residual (+ delta_scale * delta)``; without ``rows`` the sum is stored back into
         ``residual``. With ``rows`` (int32 indices) only those rows are produced."""
         n = residual.shape[0] if rows is None else (num_rows if num_rows is not None else rows.numel())
         out = ctx.buffer("norm.out", (n, self.size), self.env.dtype, residual.device)
+        if self.unit_offset or delta_scale != 1.0:
+            if self._w_f32 is None:
+                self._w_f32 = self.w_weight.float()
+            ops.add_rmsnorm_scaled(out, residual, delta, delta_scale, self._w_f32, 1.0 if self.unit_offset else 0.0, self.eps,
+                                   rows=rows, num_rows=n, write_residual=write_residual, stream=ctx.stream)
+            return out
         ops.add_rmsnorm(out, residual, delta, self.w_weight, self.eps, rows=rows, num_rows=n,
                         write_residual=write_residual, stream=ctx.stream)
         return out
@@ -60,7 +78,9 @@ class DynamicTanh(Part):
         self.w_alpha = tensors[n["alpha"]].reshape(1).contiguous()
 
     def forward(self, residual: torch.Tensor, delta: torch.Tensor | None, ctx, rows: torch.Tensor | None = None,
-                num_rows: int | None = None, write_residual: bool = True) -> torch.Tensor:
+                num_rows: int | None = None, write_residual: bool = True, delta_scale: float = 1.0) -> torch.Tensor:
+        if delta_scale != 1.0:
+            raise NotImplementedError("dynamic_tanh takes its addend unscaled")
         n = residual.shape[0] if rows is None else (num_rows if num_rows is not None else rows.numel())
         out = ctx.buffer("norm.out", (n, self.size), self.env.dtype, residual.device)
         ops.add_dyt(out, residual, delta, self.w_weight, self.w_bias, self.w_alpha, rows=rows, num_rows=n,

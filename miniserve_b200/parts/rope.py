@@ -2,6 +2,8 @@
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .base import Part, param, register_part
@@ -60,6 +62,52 @@ class RotaryPairs(RotaryNeox):
     def _frequencies(self) -> torch.Tensor:
         i = torch.arange(0, self.rotary_dim // 2, dtype=torch.float64)
         return (float(self.theta) ** (-2.0 * i / self.rotary_dim)).to(torch.float32)
+
+
+@register_part("position", "rope_yarn")
+class RotaryYarn(RotaryNeox):
+    """Rotate-half rotary encoding whose frequencies were rescaled for contexts longer than the ``original`` one:
+    with f_i = theta^(-2i / rotary_dim), pair i turns by f_i / factor * r_i + f_i * (1 - r_i), where r_i rises
+    linearly from 0 to 1 between the pair that makes ``fast`` turns over ``original`` positions (rounded down) and
+    the one that makes ``slow`` turns (rounded up): fast pairs keep their frequency, slow ones have it divided by
+    ``factor``. Cosine and sine are both multiplied by 0.1 ln(factor) + 1. Frequencies are worked out in float64 and
+    rounded once; the angle and its cosine and sine are float32 on the device. The factor on cos/sin exists only in
+    the step's table, so mixers use the kernels that read the table (``table_only``).
+    Parameters: those of ``rope_neox`` and ``factor``, ``original``, ``fast``, ``slow``."""
+    table_only = True
+
+    def __init__(self, spec, env):
+        self.factor = param(spec, "factor", float)
+        self.original = param(spec, "original", float)
+        self.fast = param(spec, "fast", float)
+        self.slow = param(spec, "slow", float)
+        if self.factor <= 0 or self.original <= 0 or self.fast <= 0 or self.slow <= 0:
+            raise ValueError("rope_yarn: factor, original, fast and slow must be positive")
+        self.magnitude = 0.1 * math.log(self.factor) + 1.0
+        super().__init__(spec, env)
+
+    def _pair_with_turns(self, turns: float) -> float:
+        return self.rotary_dim * math.log(self.original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+
+    def _frequencies(self) -> torch.Tensor:
+        i = torch.arange(0, self.rotary_dim // 2, dtype=torch.float64)
+        f = float(self.theta) ** (-2.0 * i / self.rotary_dim)
+        lo = max(math.floor(self._pair_with_turns(self.fast)), 0)
+        hi = min(math.ceil(self._pair_with_turns(self.slow)), self.rotary_dim - 1)
+        ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        return (f / self.factor * ramp + f * (1.0 - ramp)).to(torch.float32)
+
+    def step_table(self, ctx) -> torch.Tensor | None:
+        from .. import ops
+
+        if self.rotary_dim == 0:
+            return None
+        key = ("rope_table", type(self).__name__, self.theta, self.rotary_dim, self.factor, self.original, self.fast, self.slow)
+        table = ctx.step_cache.get(key)
+        if table is None:
+            table = ops.rope_table_scaled(ctx.positions, self.inv_freq, self.magnitude, ctx.num_tokens, self.rotary_dim, stream=ctx.stream)
+            ctx.step_cache[key] = table
+        return table
 
 
 @register_part("position", "none")
