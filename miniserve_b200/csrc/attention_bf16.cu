@@ -96,6 +96,34 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* ks, __nv_bfloat16* v
   }
 }
 
+// What an attention may have beyond scale, window and a sink of score 0: the score of each head's sink (the extra
+// term of the denominator is exp(sink_h), neither scaled nor capped), a cap on the scores (cap * tanh(score / cap)
+// after the scale) and a mask by blocks of `chunk` positions counted from the start of the sequence.
+struct AttnExtras {
+  const float* sink_values;  // [nq] or null
+  float cap_log2;            // cap * log2(e)
+  float cap_inv;             // scale / cap; 0: no cap
+  int chunk;                 // 0: no block mask
+};
+
+__device__ __forceinline__ float shaped_score(float s, float scale_log2, const AttnExtras& ex) {
+  return ex.cap_inv > 0.f ? ex.cap_log2 * tanhf(s * ex.cap_inv) : s * scale_log2;
+}
+// the sink's term of the denominator, in units of 2^-m
+__device__ __forceinline__ float sink_term(int sink, const AttnExtras& ex, int head, float m) {
+  if (!sink) return 0.f;
+  return exp2f((ex.sink_values ? ex.sink_values[head] * LOG2E : 0.f) - m);
+}
+
+static AttnExtras make_extras(const float* sink_values, float scale, float softcap, int chunk) {
+  AttnExtras ex;
+  ex.sink_values = sink_values;
+  ex.cap_log2 = softcap * LOG2E;
+  ex.cap_inv = softcap > 0.f ? scale / softcap : 0.f;
+  ex.chunk = chunk;
+  return ex;
+}
+
 // ------------------------------------------------------------------ prompts and mixed steps
 constexpr int PF_BM = 64, PF_BN = 64, PF_THREADS = 128;
 
@@ -104,7 +132,7 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
                     const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
                     const int* __restrict__ cu_q, const int* __restrict__ q_start, const int* __restrict__ page_indptr,
                     const int* __restrict__ page_indices, int nq, int nkv, float scale_log2, int window,
-                    int sink, int page_shift) {
+                    int sink, int page_shift, AttnExtras ex) {
   pdl_prologue();
   const int r = blockIdx.y, head = blockIdx.z;
   const int tok0 = cu_q[r], q_len = cu_q[r + 1] - tok0;
@@ -124,7 +152,8 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
   // key range this tile of queries can see
   const int q_first = start + m0, q_last = start + min(m0 + PF_BM, q_len) - 1;
   const int hi = min(kv_len, q_last + 1);
-  const int lo = window > 0 ? max(0, q_first - window + 1) : 0;
+  int lo = window > 0 ? max(0, q_first - window + 1) : 0;
+  if (ex.chunk > 0) lo = max(lo, (q_first / ex.chunk) * ex.chunk);  // the tile's first query sees furthest back
   const int tile_begin = lo / PF_BN, tile_end = (hi + PF_BN - 1) / PF_BN;
 
   // q tile
@@ -143,6 +172,7 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
   for (int i = 0; i < DTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int qpos[2] = {start + m0 + warp * 16 + g, start + m0 + warp * 16 + g + 8};
+  const int block_lo[2] = {ex.chunk > 0 ? (qpos[0] / ex.chunk) * ex.chunk : 0, ex.chunk > 0 ? (qpos[1] / ex.chunk) * ex.chunk : 0};
 
   for (int tile = tile_begin; tile < tile_end; ++tile) {
     const int stage = (tile - tile_begin) & 1;
@@ -188,8 +218,8 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
       for (int e = 0; e < 4; ++e) {
         const int key = key_base + nt * 8 + (e & 1);
         const int qp = qpos[e >> 1];
-        const bool ok = key <= qp && key >= lo && (window <= 0 || key > qp - window);
-        s[nt][e] = ok ? s[nt][e] * scale_log2 : -INFINITY;
+        const bool ok = key <= qp && key >= lo && (window <= 0 || key > qp - window) && key >= block_lo[e >> 1];
+        s[nt][e] = ok ? shaped_score(s[nt][e], scale_log2, ex) : -INFINITY;
         m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nt][e]);
       }
     float alpha[2], m_use[2];
@@ -238,8 +268,8 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
   for (int i = 0; i < 2; ++i) {
     const int row = m0 + warp * 16 + g + 8 * i;
     if (row >= q_len) continue;
-    // a sink: one more term of score 0 in the denominator, with no value
-    const float inv = 1.0f / (l_run[i] + (sink ? exp2f(-m_run[i]) : 0.f));
+    // a sink: one more term in the denominator (of score 0, or the head's own), with no value
+    const float inv = 1.0f / (l_run[i] + sink_term(sink, ex, head, m_run[i]));
     __nv_bfloat16* dst = out + ((size_t)(tok0 + row) * nq + head) * D + 2 * t;
 #pragma unroll
     for (int dt = 0; dt < DTILES; ++dt)
@@ -271,7 +301,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
                    const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ kv_len_ptr,
                    const int* __restrict__ page_indptr, const int* __restrict__ page_indices, int nq, int nkv,
                    float scale_log2, int window, int sink, int page_shift, int num_splits, int* __restrict__ counters,
-                   int cluster_merge) {
+                   int cluster_merge, AttnExtras ex) {
   // Until pdl_wait() below, only data written before this step is touched: the step's metadata and
   // the keys and values of older tokens. So the CTA may start streaming them while the kernels
   // before it (the q/k/v projection, the rotation and cache write) are still running.
@@ -282,7 +312,8 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
   const int heads_here = min(16, kvh * group + group - head0);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int kv_len = kv_len_ptr[r];
-  const int lo = window > 0 ? max(0, kv_len - window) : 0;
+  int lo = window > 0 ? max(0, kv_len - window) : 0;
+  if (ex.chunk > 0) lo = max(lo, ((kv_len - 1) / ex.chunk) * ex.chunk);  // the one query sits at position kv_len - 1
   // the key range of this split, in whole slices
   const int first_slice = lo / DC_SLICE, end_slice = (kv_len + DC_SLICE - 1) / DC_SLICE;
   const int per_split = (end_slice - first_slice + num_splits - 1) / num_splits;
@@ -375,7 +406,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
       for (int e = 0; e < 4; ++e) {
         const int key = key_base + nt * 8 + (e & 1);
         const bool ok = key >= lo && key < kv_len;
-        s[nt][e] = ok ? s[nt][e] * scale_log2 : -INFINITY;
+        s[nt][e] = ok ? shaped_score(s[nt][e], scale_log2, ex) : -INFINITY;
         m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nt][e]);
       }
     float alpha[2], m_use[2], row_sum[2] = {0.f, 0.f};
@@ -479,7 +510,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
           l += wgt * ls[i];
         }
       }
-      if (sink) l += exp2f(-m);
+      l += sink_term(sink, ex, head0 + row, m);
       out[((size_t)r * nq + head0 + row) * D + c] = __float2bfloat16_rn(acc / l);
     }
     cluster.sync();  // shared memory lives until every CTA of the cluster has read it
@@ -501,7 +532,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
     }
     const int head = head0 + row;
     if (num_splits == 1) {
-      if (sink) l += exp2f(-m);
+      l += sink_term(sink, ex, head, m);
       out[((size_t)r * nq + head) * D + c] = __float2bfloat16_rn(acc / l);
     } else {
       const size_t p = ((size_t)r * nq + head) * num_splits + split;
@@ -559,14 +590,14 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
         l += wgt * mls[i].y;
       }
     }
-    if (sink) l += exp2f(-m);
+    l += sink_term(sink, ex, head0 + row, m);
     out[item * D + c] = __float2bfloat16_rn(acc / l);
   }
 }
 
 // out[r, head] = sum_s w_s O_s / sum_s w_s l_s with w_s = 2^(m_s - max m)
 __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
-                                         const float* __restrict__ part_ml, int num_splits, int sink) {
+                                         const float* __restrict__ part_ml, int num_splits, int sink, int nq, AttnExtras ex) {
   pdl_prologue();
   const size_t item = blockIdx.x;  // r * nq + head
   const float* ml = part_ml + item * num_splits * 2;
@@ -580,7 +611,7 @@ __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, const 
       acc += wgt * part_o[(item * num_splits + s) * D + c];
       l += wgt * ml[2 * s + 1];
     }
-    if (sink) l += exp2f(-m);
+    l += sink_term(sink, ex, (int)(item % nq), m);
     out[item * D + c] = __float2bfloat16_rn(acc / l);
   }
 }
@@ -607,8 +638,9 @@ static int shift_of(int page_size) {
 MS_EXPORT int MS_ATTN_FN(prefill)(void* out, const void* q, const void* k_pool, const void* v_pool, const int* cu_q,
                                   const int* q_start, const int* page_indptr, const int* page_indices, int num_rows,
                                   int max_q_len, int nq, int nkv, float scale, int window, int sink, int page_size,
-                                  cudaStream_t stream) {
+                                  cudaStream_t stream, const float* sink_values, float softcap, int chunk) {
   if (num_rows == 0) return 0;
+  MS_CHECK_ARG(softcap >= 0.f && chunk >= 0, "attention: softcap=%g and chunk=%d must not be negative", softcap, chunk);
   MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
   MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "attention: page_size=%d must be a power of two", page_size);
   MS_CHECK_ARG(num_rows <= 65535 && nq <= 65535, "attention: too many rows (%d) or heads (%d) for one launch", num_rows, nq);
@@ -624,7 +656,8 @@ MS_EXPORT int MS_ATTN_FN(prefill)(void* out, const void* q, const void* k_pool, 
   dim3 grid(ceil_div(max_q_len, PF_BM), num_rows, nq);
   MS_LAUNCH(attn_prefill_kernel, grid, PF_THREADS, smem, stream,
       (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, cu_q,
-      q_start, page_indptr, page_indices, nq, nkv, scale * LOG2E, window, sink, shift_of(page_size));
+      q_start, page_indptr, page_indices, nq, nkv, scale * LOG2E, window, sink || sink_values != nullptr, shift_of(page_size),
+      make_extras(sink_values, scale, softcap, chunk));
   MS_CHECK_LAUNCH();
   return 0;
 }
@@ -632,7 +665,8 @@ MS_EXPORT int MS_ATTN_FN(prefill)(void* out, const void* q, const void* k_pool, 
 MS_EXPORT int MS_ATTN_FN(decode_fused)(void* out, void* part_o, void* part_ml, int* counters, const void* q,
                                        const void* k_pool, const void* v_pool, const int* kv_len,
                                        const int* page_indptr, const int* page_indices, int num_rows, int nq, int nkv,
-                                       float scale, int window, int sink, int page_size, int num_splits, cudaStream_t stream);
+                                       float scale, int window, int sink, int page_size, int num_splits, cudaStream_t stream,
+                                       const float* sink_values, float softcap, int chunk);
 
 // The decode kernel's shared-memory attribute belongs to a device: set once for each.
 static int configure_decode() {
@@ -653,7 +687,7 @@ MS_EXPORT int MS_ATTN_FN(decode)(void* out, void* part_o, void* part_ml, const v
                                  const int* page_indices, int num_rows, int nq, int nkv, float scale, int window, int sink,
                                  int page_size, int num_splits, cudaStream_t stream) {
   return MS_ATTN_FN(decode_fused)(out, part_o, part_ml, nullptr, q, k_pool, v_pool, kv_len, page_indptr, page_indices,
-                                  num_rows, nq, nkv, scale, window, sink, page_size, num_splits, stream);
+                                  num_rows, nq, nkv, scale, window, sink, page_size, num_splits, stream, nullptr, 0.f, 0);
 }
 
 // As above; with `counters` (num_rows * kv_heads * ceil(group / 16) ints, zero before the first
@@ -662,8 +696,12 @@ MS_EXPORT int MS_ATTN_FN(decode)(void* out, void* part_o, void* part_ml, const v
 MS_EXPORT int MS_ATTN_FN(decode_fused)(void* out, void* part_o, void* part_ml, int* counters, const void* q,
                                        const void* k_pool, const void* v_pool, const int* kv_len,
                                        const int* page_indptr, const int* page_indices, int num_rows, int nq, int nkv,
-                                       float scale, int window, int sink, int page_size, int num_splits, cudaStream_t stream) {
+                                       float scale, int window, int sink, int page_size, int num_splits, cudaStream_t stream,
+                                       const float* sink_values, float softcap, int chunk) {
   if (num_rows == 0) return 0;
+  MS_CHECK_ARG(softcap >= 0.f && chunk >= 0, "attention: softcap=%g and chunk=%d must not be negative", softcap, chunk);
+  sink = sink || sink_values != nullptr;
+  const AttnExtras ex = make_extras(sink_values, scale, softcap, chunk);
   MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
   MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "attention: page_size=%d must be a power of two", page_size);
   MS_CHECK_ARG(num_splits >= 1 && num_splits <= 65535, "attention: bad split count %d", num_splits);
@@ -675,10 +713,10 @@ MS_EXPORT int MS_ATTN_FN(decode_fused)(void* out, void* part_o, void* part_ml, i
   MS_LAUNCH(attn_decode_kernel, grid, DC_THREADS, DecodeSmem::bytes, stream,
       (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
       (const __nv_bfloat16*)v_pool, kv_len, page_indptr, page_indices, nq, nkv, scale * LOG2E, window, sink,
-      shift_of(page_size), num_splits, counters, 0);
+      shift_of(page_size), num_splits, counters, 0, ex);
   if (num_splits > 1 && counters == nullptr) {
     MS_LAUNCH(attn_decode_merge_kernel, num_rows * nq, D >= 128 ? 128 : 64, 0, stream, (__nv_bfloat16*)out,
-              (const float*)part_o, (const float*)part_ml, num_splits, sink);
+              (const float*)part_o, (const float*)part_ml, num_splits, sink, nq, ex);
   }
   return 0;
 }
@@ -688,8 +726,12 @@ MS_EXPORT int MS_ATTN_FN(decode_fused)(void* out, void* part_o, void* part_ml, i
 // distributed shared memory, so no scratch, no fence and no ticket are needed.
 MS_EXPORT int MS_ATTN_FN(decode_cluster)(void* out, const void* q, const void* k_pool, const void* v_pool, const int* kv_len,
                                          const int* page_indptr, const int* page_indices, int num_rows, int nq, int nkv,
-                                         float scale, int window, int sink, int page_size, int num_splits, cudaStream_t stream) {
+                                         float scale, int window, int sink, int page_size, int num_splits, cudaStream_t stream,
+                                         const float* sink_values, float softcap, int chunk) {
   if (num_rows == 0) return 0;
+  MS_CHECK_ARG(softcap >= 0.f && chunk >= 0, "attention: softcap=%g and chunk=%d must not be negative", softcap, chunk);
+  sink = sink || sink_values != nullptr;
+  const AttnExtras ex = make_extras(sink_values, scale, softcap, chunk);
   MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
   MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "attention: page_size=%d must be a power of two", page_size);
   MS_CHECK_ARG(num_splits >= 2 && num_splits <= 8, "attention: a cluster takes 2 to 8 splits, not %d", num_splits);
@@ -700,7 +742,7 @@ MS_EXPORT int MS_ATTN_FN(decode_cluster)(void* out, const void* q, const void* k
   MS_LAUNCH_CLUSTERED(attn_decode_kernel, grid, DC_THREADS, DecodeSmem::bytes, stream, num_splits,
       (__nv_bfloat16*)out, (float*)nullptr, (float*)nullptr, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
       (const __nv_bfloat16*)v_pool, kv_len, page_indptr, page_indices, nq, nkv, scale * LOG2E, window, sink,
-      shift_of(page_size), num_splits, (int*)nullptr, 1);
+      shift_of(page_size), num_splits, (int*)nullptr, 1, ex);
   return 0;
 }
 

@@ -533,11 +533,13 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
                           ctx.page_indices[group], scale, window, ctx.status, stream=ctx.stream, sink=sink, extras=extras)
         return
     recorder = getattr(ctx, "recorder", None)
-    if recorder is not None and q.dtype == torch.bfloat16 and (attention_tc_ok(q, k_pool) or attention_bf16.supports(q.shape[2], k_pool.shape[2])):
+    split_ok = q.dtype == torch.bfloat16 and attention_bf16.supports(q.shape[2], k_pool.shape[2])
+    tc_ok = q.dtype == torch.bfloat16 and extras is None and attention_tc_ok(q, k_pool)  # the tcgen05 kernel takes none of the extras
+    if recorder is not None and (tc_ok or split_ok):
         # The pass is being captured into CUDA graphs. Which tensor-core kernels run here, their grids and
         # their key splits depend on each row's length and start, which a graph cannot hold.
         single = ctx.leading_single_rows
-        if attention_tc_ok(q, k_pool) and single == recorder.single_rows and (single == 0 or attention_bf16.supports(q.shape[2], k_pool.shape[2])):
+        if tc_ok and single == recorder.single_rows and (single == 0 or split_ok):
             # Steps of this shape have `single` decoding rows at the front and prompt rows behind them. The
             # decoding rows go to the split-key kernel as inside a decode graph (its launch follows their
             # number alone). The prompt rows go to the tcgen05 kernel, launched with a CTA per SM and
@@ -555,25 +557,24 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
             return
         # Else the call is left out of the graphs and made again for every step that replays them, with
         # that step's context (the operand tensors are the captured pass's own and do not move).
-        recorder.defer(lambda step: attention(out, q, k_pool, v_pool, step, group, scale, window, sink))
+        recorder.defer(lambda step: attention(out, q, k_pool, v_pool, step, group, scale, window, sink, extras))
         return
     if q.dtype == torch.bfloat16:
         # rows at the front that bring one token each (a decode step, or the decoding requests
         # of a mixed step) go to the split-key kernel, the rest to a tiled kernel
-        split_ok = attention_bf16.supports(q.shape[2], k_pool.shape[2])
         single = ctx.leading_single_rows if split_ok else 0
         if single:
-            attention_bf16.run_decode(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink)
+            attention_bf16.run_decode(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink, extras)
         if single == ctx.num_rows:
             return
-        if attention_tc_ok(q, k_pool):
+        if tc_ok:
             attention_tc_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink)
             return
         if split_ok:
-            attention_bf16.run_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink)
+            attention_bf16.run_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink, extras)
             return
     attention_rowwise(out, q, k_pool, v_pool, ctx.positions, ctx.row_of_token, ctx.page_indptr[group],
-                      ctx.page_indices[group], scale, window, ctx.status, stream=ctx.stream, sink=sink)
+                      ctx.page_indices[group], scale, window, ctx.status, stream=ctx.stream, sink=sink, extras=extras)
 
 
 _ATTN_TC_SCRATCH_LIMIT = 1 << 29  # bytes of partial results that a step's attention may ask for

@@ -29,7 +29,14 @@ def supports(head_dim: int, page_size: int) -> bool:
 
 def takes_extras(head_dim: int, page_size: int) -> bool:
     """Whether these kernels take learned sink scores, a cap on the scores and a mask by blocks of positions."""
-    return False
+    return supports(head_dim, page_size)
+
+
+def _extras_args(extras) -> tuple:
+    if extras is None:
+        return (None, 0.0, 0)
+    sv = extras.sink_values
+    return (None if sv is None else sv.data_ptr(), float(extras.softcap or 0.0), int(extras.chunk or 0))
 
 
 def module_for(head_dim: int) -> build.Module:
@@ -45,10 +52,10 @@ def _lib(head_dim: int):
     fns = {}
     for name, args, res in (
         ("last_error", [], c_char_p),
-        ("prefill", [_p] * 8 + [_i, _i, _i, _i, _f, _i, _i, _i, _p], c_int),
+        ("prefill", [_p] * 8 + [_i, _i, _i, _i, _f, _i, _i, _i, _p, _p, _f, _i], c_int),
         ("decode", [_p] * 9 + [_i, _i, _i, _f, _i, _i, _i, _i, _p], c_int),
-        ("decode_fused", [_p] * 10 + [_i, _i, _i, _f, _i, _i, _i, _i, _p], c_int),
-        ("decode_cluster", [_p] * 7 + [_i, _i, _i, _f, _i, _i, _i, _i, _p], c_int),
+        ("decode_fused", [_p] * 10 + [_i, _i, _i, _f, _i, _i, _i, _i, _p, _p, _f, _i], c_int),
+        ("decode_cluster", [_p] * 7 + [_i, _i, _i, _f, _i, _i, _i, _i, _p, _p, _f, _i], c_int),
         ("decode_clusters_resident", [_i, ctypes.POINTER(c_int)], c_int),
     ):
         fn = getattr(lib, pre + name)
@@ -125,18 +132,18 @@ def _scratch(ctx, rows: int, nq: int, splits: int, d: int, device) -> tuple[torc
 
 
 def run(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
-        scale: float, window: int | None, sink: bool = False) -> None:
+        scale: float, window: int | None, sink: bool = False, extras=None) -> None:
     """The step's attention: rows at the front that bring one token each go to the split-key
     decode kernel, the rest to the tiled kernel."""
     single = ctx.leading_single_rows
     if single:
-        run_decode(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink)
+        run_decode(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink, extras)
     if single < ctx.num_rows:
-        run_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink)
+        run_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink, extras)
 
 
 def run_decode(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
-               scale: float, window: int | None, rows: int, sink: bool = False) -> None:
+               scale: float, window: int | None, rows: int, sink: bool = False, extras=None) -> None:
     """Rows [0, rows) of the step, one new token each (so token i belongs to row i): keys split
     across CTAs, partial results merged by the last CTA of each (row, head group) to finish."""
     t, nq, d = q.shape
@@ -151,7 +158,8 @@ def run_decode(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool:
         # the splits as one thread-block cluster: merged through distributed shared memory
         _check(fns, fns["decode_cluster"](
             out.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.kv_len.data_ptr(), indptr.data_ptr(),
-            indices.data_ptr(), rows, nq, nkv, float(scale), int(window or 0), int(sink), page_size, splits, ctx.stream))
+            indices.data_ptr(), rows, nq, nkv, float(scale), int(window or 0), int(sink), page_size, splits, ctx.stream,
+            *_extras_args(extras)))
         return
     part_o = part_ml = counters = None
     if splits > 1:
@@ -166,12 +174,12 @@ def run_decode(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool:
     _check(fns, fns["decode_fused"](
         out.data_ptr(), None if part_o is None else part_o.data_ptr(), None if part_ml is None else part_ml.data_ptr(),
         None if counters is None else counters.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.kv_len.data_ptr(), indptr.data_ptr(),
-        indices.data_ptr(), rows, nq, nkv, float(scale), int(window or 0), int(sink), page_size, splits, ctx.stream),
-        launches=1)
+        indices.data_ptr(), rows, nq, nkv, float(scale), int(window or 0), int(sink), page_size, splits, ctx.stream,
+        *_extras_args(extras)), launches=1)
 
 
 def run_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
-                scale: float, window: int | None, first_row: int = 0, sink: bool = False) -> None:
+                scale: float, window: int | None, first_row: int = 0, sink: bool = False, extras=None) -> None:
     """Rows [first_row, num_rows) of the step, any number of new tokens each: tiles of 64 queries
     over the row's pages (``mma.sync``; the tcgen05 kernel of ``attention_tc.cu`` takes head size 128)."""
     t, nq, d = q.shape
@@ -182,4 +190,4 @@ def run_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool
     _check(fns, fns["prefill"](
         out.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), ctx.cu_q.data_ptr() + skip, ctx.q_start.data_ptr() + skip,
         indptr.data_ptr() + skip, indices.data_ptr(), ctx.num_rows - first_row, ctx.max_q_len, nq, nkv, float(scale), int(window or 0),
-        int(sink), page_size, ctx.stream))
+        int(sink), page_size, ctx.stream, *_extras_args(extras)))
