@@ -21,7 +21,9 @@ mixed steps, their fraction of the measured peaks, and the number of preemptions
 ``--config fekulix`` measures the Fekulix design (random weights, the layer sizes of Qwen3-0.6B and
 Qwen3-1.7B) beside the Qwen3 model of the same width, depth, feed-forward size and vocabulary: one
 2,048-token prompt step and decode steps at batch 8 behind 2,048 tokens; ``--kernels`` adds the device
-time per kernel of both steps.
+time per kernel of both steps. ``--config mugipel`` does the same for the Mugipel design (attention layers
+with capped scores, a block mask and learned sinks in turn with latent-attention layers, the last stretch of
+layers run twice).
 """
 
 from __future__ import annotations
@@ -350,6 +352,40 @@ def fekulix_config(width: int, ff: int, runs: int, vocab: int, heads: int, kv_he
             "layers": [delta if i % 4 == 3 else par for i in range(runs)]}
 
 
+def mugipel_config(width: int, ff: int, runs: int, vocab: int, heads: int, kv_heads: int) -> dict:
+    """A Mugipel model at a real model's layer sizes: attention layers (the heads of the Qwen3 model of this width,
+    half of each head rotated with rescaled frequencies, scores capped at 50, blocks of 1,024 positions, a learned
+    sink per head) in turn with latent-attention layers (as many heads of 128, a latent of width / 8 numbers per
+    token), the last four layers run twice: ``runs`` layer runs in all."""
+    att = {"dim": 128, "heads": heads, "kv_heads": kv_heads, "mask": {"size": 1024}, "scale": 128 ** -0.5, "softcap": 50.0, "vdim": 128,
+           "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 4.0, "fast": 32.0, "original": 8192, "slow": 1.0}}}
+    lat = {"dim": 128, "heads": heads, "kv_rank": max(64, width // 8), "scale": 128 ** -0.5, "vdim": 128}
+    stored = runs - 4
+    layers = [{"type": "attention" if i % 2 == 0 else "latent_attention", "mixer": dict(att if i % 2 == 0 else lat),
+               "mlp": {"ff": ff, "kind": "dense"}} for i in range(stored)]
+    return {"architecture": "Mugipel", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "layers": layers,
+            "loop": {"start": stored - 4, "stop": stored, "times": 2}}
+
+
+def bytes_per_step_of_weights(model) -> int:
+    """Bytes of weights a step reads: every run of a layer reads that layer's tensors (a layer that runs twice
+    counts twice), plus the norm before the head, the head and the parts between layers."""
+    def of(part, seen):
+        total = 0
+        for v in vars(part).values():
+            if hasattr(v, "data_ptr") and v.dim() >= 1 and v.is_floating_point() and v.data_ptr() not in seen:
+                seen.add(v.data_ptr())
+                total += v.numel() * v.element_size()
+        for sub in part.sub_parts().values():
+            total += of(sub, seen)
+        pos = getattr(part, "position", None)
+        return total + (of(pos, seen) if pos is not None else 0)
+
+    per_layer = [of(layer, set()) for layer in model.layers]
+    extra = model.weight_bytes() - sum(per_layer)
+    return sum(per_layer[e.layer] for e in model.spec.run_order) + max(extra, 0)
+
+
 def kernel_times(run_step, repeats: int = 3) -> dict:
     """Device time per kernel name (us per step, launches per step) of ``run_step()``, from the activity
     records of torch.profiler (no counters, nothing is replayed); {} if the records cannot be had."""
@@ -378,8 +414,8 @@ def kernel_times(run_step, repeats: int = 3) -> dict:
         return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
 
 
-def run_fekulix(args) -> dict:
-    """Prefill and decode of Fekulix beside Qwen3 at equal width, depth, feed-forward and vocabulary."""
+def run_fekulix(args, design: str = "fekulix") -> dict:
+    """Prefill and decode of a design (Fekulix, Mugipel) beside Qwen3 at equal width, depth, feed-forward and vocabulary."""
     import torch
 
     from miniserve_b200.config import preset
@@ -387,27 +423,28 @@ def run_fekulix(args) -> dict:
     from miniserve_b200.engine.step import StepRow
 
     peaks = load_peaks()
-    out = {"impl": "ours", "config": "fekulix", "dtype": "bf16", "data": "synthetic (random-init weights, uniform token ids)",
+    make = {"fekulix": fekulix_config, "mugipel": mugipel_config}[design]
+    out = {"impl": "ours", "config": design, "dtype": "bf16", "data": "synthetic (random-init weights, uniform token ids)",
            "batch": args.batch, "context": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "peaks": peaks["source"], "sizes": {}}
     steps = min(args.steps, 64)
     for size in ("0.6b", "1.7b"):
         q = preset(size)
         if args.layers is not None:
             q["num_hidden_layers"] = args.layers
-        f = fekulix_config(q["hidden_size"], q["intermediate_size"], q["num_hidden_layers"], q["vocab_size"],
-                           q["num_attention_heads"], q["num_key_value_heads"])
+        f = make(q["hidden_size"], q["intermediate_size"], q["num_hidden_layers"], q["vocab_size"],
+                 q["num_attention_heads"], q["num_key_value_heads"])
         entry = {}
-        for name, raw in (("fekulix", f), ("qwen3", q)):
+        for name, raw in ((design, f), ("qwen3", q)):
             llm = LLM(random=raw, weights_seed=0, dtype="bfloat16", kv_pool_tokens=10 * (CONTEXT + steps + 64) + 4096, page_size=16,
                       max_running=16, chunked_prefill_size=2048, cuda_graph=not args.no_graph)
             eng = llm.engine
             ms, launches, mean_ctx = time_decode(eng, args.batch, CONTEXT, steps, args.warmup)
             pre_ms = time_prefill(eng, PREFILL_TOKENS)
-            step_bytes = llm.model.weight_bytes() + args.batch * (mean_ctx * eng.cache.bytes_per_token() + 2 * eng.cache.state_bytes() / (eng.cache.max_requests + 1))
+            step_bytes = bytes_per_step_of_weights(llm.model) + args.batch * (mean_ctx * eng.cache.bytes_per_token() + 2 * eng.cache.state_bytes() / (eng.cache.max_requests + 1))
             res = {"decode_tok_s": round(args.batch * 1000.0 / ms, 1), "decode_ms": round(ms, 4), "decode_launches": round(launches, 1),
                    "decode_hbm_frac": round(step_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
                    "prefill_tok_s": round(PREFILL_TOKENS * 1000.0 / pre_ms, 1), "prefill_ms": round(pre_ms, 4),
-                   "weight_bytes": llm.model.weight_bytes()}
+                   "weight_bytes": llm.model.weight_bytes(), "weight_bytes_per_step": bytes_per_step_of_weights(llm.model)}
             if args.kernels:
                 rng = random.Random(3)
                 ids = [rng.randrange(q["vocab_size"]) for _ in range(PREFILL_TOKENS)]
@@ -426,8 +463,8 @@ def run_fekulix(args) -> dict:
             entry[name] = res
             del llm, eng
             torch.cuda.empty_cache()
-        entry["decode_ratio"] = round(entry["fekulix"]["decode_tok_s"] / entry["qwen3"]["decode_tok_s"], 3)
-        entry["prefill_ratio"] = round(entry["fekulix"]["prefill_tok_s"] / entry["qwen3"]["prefill_tok_s"], 3)
+        entry["decode_ratio"] = round(entry[design]["decode_tok_s"] / entry["qwen3"]["decode_tok_s"], 3)
+        entry["prefill_ratio"] = round(entry[design]["prefill_tok_s"] / entry["qwen3"]["prefill_tok_s"], 3)
         out["sizes"][size] = entry
     return out
 
@@ -604,10 +641,10 @@ def main() -> int:
     ap.add_argument("--no-graph", action="store_true", help="run decode steps without CUDA graphs")
     ap.add_argument("--profile-range", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
-    ap.add_argument("--config", choices=["0.6b", "8b", "32b", "fekulix"], default="0.6b",
+    ap.add_argument("--config", choices=["0.6b", "8b", "32b", "fekulix", "mugipel"], default="0.6b",
                     help="0.6b: the benchmark line; 8b, 32b: the larger workloads through Engine.generate (a line of their own); "
-                         "fekulix: prefill and decode of the Fekulix design beside Qwen3 at equal sizes (a line of its own)")
-    ap.add_argument("--kernels", action="store_true", help="with --config fekulix: also device time per kernel of a prompt step and a decode step")
+                         "fekulix, mugipel: prefill and decode of that design beside Qwen3 at equal sizes (a line of its own)")
+    ap.add_argument("--kernels", action="store_true", help="with --config fekulix or mugipel: also device time per kernel of a prompt step and a decode step")
     ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                     help="measure only the decode steps or only the prefill (for profiling); the line then lacks the other parts")
     args = ap.parse_args()
@@ -620,8 +657,8 @@ def main() -> int:
         args.warmup = 3
     global PROFILE_RANGE
     PROFILE_RANGE = args.profile_range
-    if args.config == "fekulix" and args.impl == "ours":
-        result = run_fekulix(args)
+    if args.config in ("fekulix", "mugipel") and args.impl == "ours":
+        result = run_fekulix(args, args.config)
     elif args.config != "0.6b" and args.impl == "ours":
         result = run_workload(args)
     else:

@@ -469,6 +469,10 @@ int launch_scan(int num_rows, int H, int dk, int dv, Args... args) {
 
 using namespace ms;
 
+MS_DEFINE_LAST_ERROR(ms_recurrence_last_error)
+MS_DEFINE_PDL_SWITCH(ms_recurrence_set_pdl)
+
+
 // in_dtype: of q, k, v; z_dtype: of z and beta. delta: 0 decay rule, 1 delta rule. z_is_decay: z and beta are
 // float32 and hold the decays and sigmoid(beta) themselves (ms_decay_from_logits), not their logits.
 MS_EXPORT int ms_decay_scan(float* o_out, float* state, const void* q, int ld_q, const void* k, int ld_k, int qk_group,

@@ -70,5 +70,5 @@ def add_model_args(parser: argparse.ArgumentParser) -> None:
     g = parser.add_argument_group("model")
     g.add_argument("--model", default=None, help="a model folder: config.json and safetensors files")
     g.add_argument("--random", default=None, metavar="PRESET",
-                   help="no folder: a model of these sizes with random weights (tiny-a, tiny-b, 0.6b, 1.7b, 8b, 32b, fekulix-tiny)")
+                   help="no folder: a model of these sizes with random weights (tiny-a, tiny-b, 0.6b, 1.7b, 8b, 32b, fekulix-tiny, mugipel-tiny)")
     g.add_argument("--weights-seed", type=int, default=0, help="the random weights are drawn from this seed")

@@ -23,9 +23,8 @@ def _position(c) -> PartSpec:
     if not rot or int(rot["dims"]) == 0:
         return PartSpec("none")
     params = dict(head_dim=int(c["dim"]), theta=float(rot["base"]), rotary_dim=int(rot["dims"]))
-    scaling = rot.get("scaling")
-    if not scaling:
-        return PartSpec("rope_neox", params)
+    # without rescaling: a factor of one leaves every frequency and the factor on cos and sin as they are
+    scaling = rot.get("scaling") or {"factor": 1.0, "original": 1.0, "fast": 1.0, "slow": 1.0}
     params.update(factor=float(scaling["factor"]), original=float(scaling["original"]), fast=float(scaling["fast"]),
                   slow=float(scaling["slow"]))
     return PartSpec("rope_yarn", params)

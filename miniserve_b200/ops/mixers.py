@@ -123,11 +123,11 @@ def decay_scan(o_out, state, q, k, v, z, z_bias, decay_coef, z_sign: float, beta
         # (a decode step, one token a row, works them out while it stages the token)
         width = heads * dk + (heads if beta is not None else 0)
         pre = ctx.buffer("scan.decay", (t, width), torch.float32, o_out.device)
-        native.mixers_check(native.mixers().ms_decay_from_logits(
+        native.recurrence_check(native.recurrence().ms_decay_from_logits(
             _ptr(pre), _ptr(z), _rows(z), _ptr(z_bias), _ptr(decay_coef), float(z_sign), _ptr(beta),
             0 if beta is None else _rows(beta), t, heads, dk, _dt(z.dtype), ctx.stream))
         z, beta, ready = pre[:, :heads * dk], (pre[:, heads * dk:] if beta is not None else None), 1
-    native.mixers_check(native.mixers().ms_decay_scan(
+    native.recurrence_check(native.recurrence().ms_decay_scan(
         _ptr(o_out), _ptr(state), _ptr(q), _rows(q), _ptr(k), _rows(k), heads // groups, _ptr(v), _rows(v), _ptr(z), _rows(z),
         _ptr(z_bias), _ptr(decay_coef), float(z_sign), ready, _ptr(beta), 0 if beta is None else _rows(beta), _ptr(ctx.cu_q),
         _ptr(ctx.q_start), _ptr(ctx.state_slot), ctx.num_rows, heads, dk, dv, float(q_scale), int(delta), _dt(q.dtype),
@@ -143,7 +143,7 @@ def conv_silu_unit(out, x, conv_state, weight, ctx, unit_heads: int, dk: int, ot
     _f32(out, weight)
     assert x.shape == (t, c) and weight.shape[0] == c and conv_state.dtype == x.dtype and conv_state.is_contiguous()
     assert conv_state.shape[1:] == (max(taps - 1, 0), c)
-    native.mixers_check(native.mixers().ms_conv_silu_unit(
+    native.recurrence_check(native.recurrence().ms_conv_silu_unit(
         _ptr(out), _ptr(x), _rows(x), _ptr(conv_state), _ptr(weight), _ptr(ctx.row_of_token), _ptr(ctx.cu_q), _ptr(ctx.q_start),
         _ptr(ctx.state_slot), t, c, taps, unit_heads, dk, other_heads, dv, float(unit_eps), _dt(x.dtype), ctx.stream))
 
@@ -152,7 +152,7 @@ def conv_state_update(conv_state, x, ctx, taps: int) -> None:
     """Each row's slot of ``conv_state`` [slots, taps - 1, C] becomes the last taps - 1 inputs ``x`` [T, C]
     of its sequence after this step (older entries move up when the portion is shorter than that)."""
     assert conv_state.dtype == x.dtype and conv_state.is_contiguous()
-    native.mixers_check(native.mixers().ms_conv_state_update(
+    native.recurrence_check(native.recurrence().ms_conv_state_update(
         _ptr(conv_state), _ptr(x), _rows(x), _ptr(ctx.cu_q), _ptr(ctx.q_start), _ptr(ctx.state_slot), ctx.num_rows, x.shape[1],
         taps, _dt(x.dtype), ctx.stream))
 
@@ -168,29 +168,29 @@ def _decay_scan_segmented(o_out, state, q, k, v, z, z_bias, decay_coef, z_sign, 
     from types import SimpleNamespace
 
     t, dev, p, rows = o_out.shape[0], o_out.device, SEGMENTS, ctx.num_rows
-    lib = native.mixers()
+    lib = native.recurrence()
     key = ("scan.segments", p)
     seg = ctx.step_cache.get(key) if hasattr(ctx, "step_cache") else None
     if seg is None:  # the same for every layer of the step
         ints = torch.empty(3 * rows * p + 1, dtype=torch.int32, device=dev)
         seg = (ints[:rows * p + 1], ints[rows * p + 1:2 * rows * p + 1], ints[2 * rows * p + 1:])
-        native.mixers_check(lib.ms_segment_setup(_ptr(seg[0]), _ptr(seg[1]), _ptr(seg[2]), _ptr(ctx.cu_q), rows, p, ctx.stream))
+        native.recurrence_check(lib.ms_segment_setup(_ptr(seg[0]), _ptr(seg[1]), _ptr(seg[2]), _ptr(ctx.cu_q), rows, p, ctx.stream))
         if hasattr(ctx, "step_cache"):
             ctx.step_cache[key] = seg
     seg_cu, seg_zero, seg_slot = seg
     decay = ctx.buffer("scan.decay", (t, heads * dk), torch.float32, dev)
-    native.mixers_check(lib.ms_decay_from_logits(_ptr(decay), _ptr(z), _rows(z), _ptr(z_bias), _ptr(decay_coef), float(z_sign), None, 0,
+    native.recurrence_check(lib.ms_decay_from_logits(_ptr(decay), _ptr(z), _rows(z), _ptr(z_bias), _ptr(decay_coef), float(z_sign), None, 0,
                                                  t, heads, dk, _dt(z.dtype), ctx.stream))
     ends = ctx.buffer("scan.ends", (rows * p, heads, dv, dk), torch.float32, dev)
     before = ctx.buffer("scan.before", (rows * p, heads, dv, dk), torch.float32, dev)
     cum = ctx.buffer("scan.cum", (t, heads * dk), torch.float32, dev)
     pieces = SimpleNamespace(cu_q=seg_cu, q_start=seg_zero, state_slot=seg_slot, num_rows=rows * p, stream=ctx.stream)
     groups = q.shape[1] // dk
-    native.mixers_check(lib.ms_decay_scan(
+    native.recurrence_check(lib.ms_decay_scan(
         _ptr(o_out), _ptr(ends), _ptr(q), _rows(q), _ptr(k), _rows(k), heads // groups, _ptr(v), _rows(v), _ptr(decay), _rows(decay),
         _ptr(z_bias), _ptr(decay_coef), float(z_sign), 1, None, 0, _ptr(pieces.cu_q), _ptr(pieces.q_start), _ptr(pieces.state_slot),
         pieces.num_rows, heads, dk, dv, float(q_scale), 0, _dt(q.dtype), 0, ctx.stream))
-    native.mixers_check(lib.ms_segment_finish(
+    native.recurrence_check(lib.ms_segment_finish(
         _ptr(o_out), _ptr(state), _ptr(ends), _ptr(before), _ptr(cum), _ptr(decay), _rows(decay), _ptr(q), _rows(q), heads // groups,
         _ptr(seg_cu), _ptr(ctx.q_start), _ptr(ctx.state_slot), rows, t, p, heads, dk, dv, float(q_scale), _dt(q.dtype), ctx.stream),
         launches=3)
@@ -205,7 +205,7 @@ def head_norm_gate(out, o, weight, gate, eps: float, scale: float, gate_kind: st
     t, heads, dv = o.shape
     _f32(o, weight)
     assert out.shape == (t, heads * dv) and gate.shape == (t, heads * dv) and gate.dtype == out.dtype and weight.numel() == dv
-    native.mixers_check(native.mixers().ms_head_norm_gate(
+    native.recurrence_check(native.recurrence().ms_head_norm_gate(
         _ptr(out), _rows(out), _ptr(o), _ptr(weight), _ptr(gate), _rows(gate), t, heads, dv, float(eps), float(scale),
         GATE_KINDS[gate_kind], _dt(out.dtype), _stream(stream)))
 

@@ -129,14 +129,6 @@ def mixers():
     _declare(lib, "ms_axpby", [_p, _p, _p, _f, _f, _ll, _i, _p])
     _declare(lib, "ms_head_gate", [_p, _i, _p, _p, _i, _i, _i, _i, _i, _f, _i, _p])
     _declare(lib, "ms_qkv_prepare", [_p] * 4 + [_i] * 4 + [_p] * 7 + [_i] * 8 + [_f, _i, _i, _p, _i, _p])
-    _declare(lib, "ms_decay_scan", [_p, _p, _p, _i, _p, _i, _i, _p, _i, _p, _i, _p, _p, _f, _i, _p, _i, _p, _p, _p,
-                                    _i, _i, _i, _i, _f, _i, _i, _i, _p])
-    _declare(lib, "ms_segment_setup", [_p, _p, _p, _p, _i, _i, _p])
-    _declare(lib, "ms_segment_finish", [_p, _p, _p, _p, _p, _p, _i, _p, _i, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p])
-    _declare(lib, "ms_decay_from_logits", [_p, _p, _i, _p, _p, _f, _p, _i, _i, _i, _i, _i, _p])
-    _declare(lib, "ms_conv_silu_unit", [_p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p])
-    _declare(lib, "ms_conv_state_update", [_p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p])
-    _declare(lib, "ms_head_norm_gate", [_p, _i, _p, _p, _p, _i, _i, _i, _i, _f, _f, _i, _i, _p])
     _declare(lib, "ms_add_rmsnorm_scaled", [_p, _p, _p, _f, _p, _f, _p, _f, _i, _i, _i, _i, _p])
     _declare(lib, "ms_stream_concat", [_p, _p, _p, _f, _p, _p, _i, _i, _i, _i, _i, _i, _p])
     _declare(lib, "ms_add_row_vector", [_p, _p, _i, _i, _p])
@@ -145,6 +137,27 @@ def mixers():
     _declare(lib, "ms_rope_table_scaled", [_p, _p, _p, _f, _i, _i, _p])
     _declare(lib, "ms_latent_prepare", [_p, _p, _i, _i, _p, _f, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _p])
     return lib
+
+
+@lru_cache(maxsize=None)
+def recurrence():
+    lib = ctypes.CDLL(str(build.ensure_built(build.RECURRENCE)))
+    _declare(lib, "ms_recurrence_last_error", [], c_char_p)
+    _declare(lib, "ms_recurrence_set_pdl", [_i], None)
+    lib.ms_recurrence_set_pdl(int(pdl_enabled()))
+    _declare(lib, "ms_decay_scan", [_p, _p, _p, _i, _p, _i, _i, _p, _i, _p, _i, _p, _p, _f, _i, _p, _i, _p, _p, _p,
+                                    _i, _i, _i, _i, _f, _i, _i, _i, _p])
+    _declare(lib, "ms_segment_setup", [_p, _p, _p, _p, _i, _i, _p])
+    _declare(lib, "ms_segment_finish", [_p, _p, _p, _p, _p, _p, _i, _p, _i, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p])
+    _declare(lib, "ms_decay_from_logits", [_p, _p, _i, _p, _p, _f, _p, _i, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_conv_silu_unit", [_p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p])
+    _declare(lib, "ms_conv_state_update", [_p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_head_norm_gate", [_p, _i, _p, _p, _p, _i, _i, _i, _i, _f, _f, _i, _i, _p])
+    return lib
+
+
+def recurrence_check(rc: int, launches: int = 1) -> None:
+    kernel_check(rc, lib=recurrence() if rc else None, errfn="ms_recurrence_last_error", launches=launches)
 
 
 def mixers_check(rc: int, launches: int = 1) -> None:
