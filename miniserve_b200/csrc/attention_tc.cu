@@ -184,6 +184,19 @@ __device__ __forceinline__ bool at_group_any(int id, bool flag) {
   return res != 0;
 }
 
+// What an attention may have beyond scale, window and a sink of score 0: the score of each head's sink, a cap on
+// the scores and a mask by blocks of positions (the block size travels in AtGrid, with the window). The cap works on
+// the raw products, before the scale: s' = (cap / scale) tanh(s scale / cap), so that s' scale is the capped score
+// and everything after it is as without a cap. tanh(y) = 1 - 2 / (1 + 2^(2 y log2 e)), absolute error about 1e-6.
+struct AtExtras {
+  const float* sink_values;  // [nq] or null
+  float cap_raw;             // cap / scale
+  float cap_c2;              // 2 log2(e) scale / cap; 0: no cap
+};
+__device__ __forceinline__ float at_cap(float s, float cap_raw, float cap_c2) {
+  return cap_raw * (1.f - __fdividef(2.f, 1.f + at_ex2(s * cap_c2)));
+}
+
 // A new running maximum for a row: the stale one is kept while the new one exceeds it by at most
 // 2^8 after scaling (the same maximum scales the sum, so the result stays exact); returns the factor
 // that what was accumulated so far has to be scaled by (1: nothing to do).
@@ -220,7 +233,7 @@ __device__ __forceinline__ void at_rescale(uint32_t t_o, float alpha) {
 // 128 live values cost the kernel around the call more than the second read costs here.
 // Returns the sum of the row's exponentials.
 __device__ __noinline__ float at_softmax_masked(uint32_t t_s, uint32_t t_o, int seen_lo, int seen_hi, float scale_log2,
-                                                float& m_used, float& l_sum) {
+                                                float& m_used, float& l_sum, float cap_raw, float cap_c2) {
   float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll 1
   for (int c = 0; c < 4; ++c) {
@@ -230,7 +243,8 @@ __device__ __noinline__ float at_softmax_masked(uint32_t t_s, uint32_t t_o, int 
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       const int off = c * 32 + i;
-      mx[i & 3] = fmaxf(mx[i & 3], off <= seen_hi && off >= seen_lo ? v[i] : -INFINITY);
+      const float sc = cap_c2 > 0.f ? at_cap(v[i], cap_raw, cap_c2) : v[i];
+      mx[i & 3] = fmaxf(mx[i & 3], off <= seen_hi && off >= seen_lo ? sc : -INFINITY);
     }
   }
   const float alpha = at_new_maximum(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), m_used, scale_log2);
@@ -246,6 +260,10 @@ __device__ __noinline__ float at_softmax_masked(uint32_t t_s, uint32_t t_o, int 
     at_tmem_ld32(t_s + (uint32_t)(c * 32), v);
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
     uint32_t pk[16];
+    if (cap_c2 > 0.f) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = at_cap(v[i], cap_raw, cap_c2);
+    }
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
       const int off = c * 32 + i;
@@ -272,6 +290,7 @@ struct AtItem {
 
 struct AtGrid {
   int q_tiles, rows, head_groups, splits, max_tiles_per_item, window, G;
+  int chunk;  // > 0: a query sees only keys from the start of its own block of this many positions on
   __device__ __forceinline__ int total() const { return q_tiles * rows * head_groups * splits; }
 };
 
@@ -300,6 +319,10 @@ __device__ __forceinline__ bool at_item(AtItem& it, int idx, const AtGrid& gr, c
     it.q_last[g] = it.start + min(it.m0 + (g + 1) * tpc, it.q_len) - 1;
     it.lo_g[g] = gr.window > 0 ? max(0, it.q_first[g] - gr.window + 1) : 0;
     it.lo_max[g] = gr.window > 0 ? max(0, it.q_last[g] - gr.window + 1) : 0;
+    if (gr.chunk > 0) {  // the first query's block starts earliest, the last query's latest
+      it.lo_g[g] = max(it.lo_g[g], (it.q_first[g] / gr.chunk) * gr.chunk);
+      it.lo_max[g] = max(it.lo_max[g], (it.q_last[g] / gr.chunk) * gr.chunk);
+    }
   }
   it.tile_begin = it.lo_g[0] / AT_KEYS;
   it.n_tiles[0] = (min(it.kv_len, it.q_last[0] + 1) + AT_KEYS - 1) / AT_KEYS - it.tile_begin;
@@ -362,7 +385,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         const int* __restrict__ page_indices, int nq, int nkv, float scale_log2, int sink, int page_shift,
                         const AtGrid gr_given, int* __restrict__ status,
                         float* __restrict__ part_o, float2* __restrict__ part_ml, int* __restrict__ queue,
-                        int* __restrict__ tickets, const int* __restrict__ plan) {
+                        int* __restrict__ tickets, const int* __restrict__ plan, const AtExtras ex) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], p_full[2], o_final[2];
@@ -567,6 +590,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int tok_in_req = m0 + g * tpc + tok;
         const int qpos = start + tok_in_req;
         const int lo_mine = it.lo_g[g], lo_max_mine = it.lo_max[g], q_first_mine = it.q_first[g];
+        const int block_lo = gr.chunk > 0 ? (qpos / gr.chunk) * gr.chunk : 0;
+        // the sink's score in units of log2 (it is neither scaled nor capped)
+        const float sink_l2 = ex.sink_values != nullptr ? ex.sink_values[head0 + hd] * AT_LOG2E : 0.f;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t t_s = tmem + (uint32_t)(g * 128) + lane_base, t_o = tmem + (uint32_t)(256 + g * 128) + lane_base;
         const int n_mine = it.n_tiles[g];
@@ -585,6 +611,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   #pragma unroll
             for (int c = 0; c < 4; ++c) at_tmem_ld32(t_s + (uint32_t)(c * 32), sv[c]);
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            if (ex.cap_c2 > 0.f) {
+  #pragma unroll
+              for (int c = 0; c < 4; ++c)
+  #pragma unroll
+                for (int i = 0; i < 32; ++i) sv[c][i] = at_cap(sv[c][i], ex.cap_raw, ex.cap_c2);
+            }
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
   #pragma unroll
             for (int c = 0; c < 4; ++c)
@@ -615,8 +647,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // a tile on the diagonal, at a window's edge or at the request's end: the keys of the tile
             // that this row sees are those at offsets [seen_lo, seen_hi]
             const int seen_hi = qpos - key0;
-            const int seen_lo = max(lo_mine, window > 0 ? qpos - window + 1 : 0) - key0;
-            part[0] = at_softmax_masked(t_s, t_o, seen_lo, seen_hi, scale_log2, m_used, l_sum);
+            const int seen_lo = max(max(lo_mine, block_lo), window > 0 ? qpos - window + 1 : 0) - key0;
+            part[0] = at_softmax_masked(t_s, t_o, seen_lo, seen_hi, scale_log2, m_used, l_sum, ex.cap_raw, ex.cap_c2);
           }
           l_sum += (part[0] + part[1]) + (part[2] + part[3]);
           const int valid_keys = kv_len - key0;
@@ -644,7 +676,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (it.shares[g] <= 1) {
           if (ok && n_mine > 0) {
             // a sink: one more term of score 0 in the denominator, with no value
-            const float inv = 1.0f / (l_sum + (sink ? at_ex2(-m_used * scale_log2) : 0.f));
+            const float inv = 1.0f / (l_sum + (sink ? at_ex2(sink_l2 - m_used * scale_log2) : 0.f));
   #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
               float ov[32];
@@ -716,7 +748,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               const float2 ml = sp == split ? make_float2(m_used, l_sum) : __ldcg(&pml[sp * 128]);
               l_all += ml.y == 0.f ? 0.f : at_ex2((ml.x - m_all) * scale_log2) * ml.y;
             }
-            if (sink) l_all += at_ex2(-m_all * scale_log2);
+            if (sink) l_all += at_ex2(sink_l2 - m_all * scale_log2);
             const float inv = 1.0f / l_all;
   #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
@@ -861,7 +893,13 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
                                  const int* q_start, const int* page_indptr, const int* page_indices, int num_rows,
                                  int num_tokens, int max_q_len, int nq, int nkv, long long pool_pages, float scale,
                                  int window, int sink, int page_size, int* status, int splits, int min_tiles, float* partials,
-                                 int* queue, const int* plan, cudaStream_t stream) {
+                                 int* queue, const int* plan, cudaStream_t stream, const float* sink_values, float softcap, int chunk) {
+  MS_CHECK_ARG(softcap >= 0.f && chunk >= 0, "attention_tc: softcap=%g and chunk=%d must not be negative", softcap, chunk);
+  sink = sink || sink_values != nullptr;
+  AtExtras ex;
+  ex.sink_values = sink_values;
+  ex.cap_raw = softcap > 0.f ? softcap / scale : 0.f;
+  ex.cap_c2 = softcap > 0.f ? 2.f * AT_LOG2E * scale / softcap : 0.f;
   // plan: null, or four device ints (tiles of queries per row, rows, key splits, least key tiles per split) that
   // ms_attn_tc_write_plan fills before the launch runs; num_rows, max_q_len, splits and min_tiles are then unused
   if (num_rows == 0 && plan == nullptr) return 0;
@@ -920,7 +958,7 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
     MS_CHECK_CUDA(cudaGetDevice(&dev));
     MS_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
-  const AtGrid gr = {ceil_div(max_q_len, 2 * tpc), num_rows, nq / G, splits, min_tiles, window, G};
+  const AtGrid gr = {ceil_div(max_q_len, 2 * tpc), num_rows, nq / G, splits, min_tiles, window, G, chunk};
   const long long total = (long long)gr.q_tiles * gr.rows * gr.head_groups * gr.splits;
   MS_CHECK_ARG(total < (1LL << 30), "attention_tc: %lld work items are too many for one launch", total);
   // one CTA fills an SM (192 KB of shared memory, all of tensor memory) and takes items until none is left
@@ -928,7 +966,7 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
   MS_LAUNCH(attn_prefill_tc_kernel, grid, AT_THREADS, smem_bytes, stream, map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q,
             q_start, page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, sink, page_shift, gr, status,
             partials, reinterpret_cast<float2*>(partials + (total / gr.splits) * 2 * gr.splits * (AT_ROWS * AT_D)), queue,
-            queue + 2, plan);
+            queue + 2, plan, ex);
   return 0;
 }
 

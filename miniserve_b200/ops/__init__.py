@@ -534,7 +534,7 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
         return
     recorder = getattr(ctx, "recorder", None)
     split_ok = q.dtype == torch.bfloat16 and attention_bf16.supports(q.shape[2], k_pool.shape[2])
-    tc_ok = q.dtype == torch.bfloat16 and extras is None and attention_tc_ok(q, k_pool)  # the tcgen05 kernel takes none of the extras
+    tc_ok = q.dtype == torch.bfloat16 and attention_tc_ok(q, k_pool)
     if recorder is not None and (tc_ok or split_ok):
         # The pass is being captured into CUDA graphs. Which tensor-core kernels run here, their grids and
         # their key splits depend on each row's length and start, which a graph cannot hold.
@@ -549,11 +549,11 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
                 inside = ctx.graph_bucket
                 ctx.graph_bucket = ctx.graph_bucket or single
                 try:
-                    attention_bf16.run_decode(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink)
+                    attention_bf16.run_decode(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink, extras)
                 finally:
                     ctx.graph_bucket = inside
             if single < ctx.num_rows:
-                _attention_tc_planned(out, q, k_pool, v_pool, ctx, group, scale, window, recorder, single, sink)
+                _attention_tc_planned(out, q, k_pool, v_pool, ctx, group, scale, window, recorder, single, sink, extras)
             return
         # Else the call is left out of the graphs and made again for every step that replays them, with
         # that step's context (the operand tensors are the captured pass's own and do not move).
@@ -568,7 +568,7 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
         if single == ctx.num_rows:
             return
         if tc_ok:
-            attention_tc_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink)
+            attention_tc_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink, extras)
             return
         if split_ok:
             attention_bf16.run_prefill(out, q, k_pool, v_pool, ctx, group, scale, window, single, sink, extras)
@@ -591,8 +591,14 @@ def attention_tc_ok(q: torch.Tensor, k_pool: torch.Tensor) -> bool:
 _ATTN_TC_PLANNED_SCRATCH = 1 << 25  # floats of partial results that a captured launch may use (128 MB)
 
 
+def _extras_args(extras) -> tuple:
+    if extras is None:
+        return (None, 0.0, 0)
+    return (_ptr(extras.sink_values), float(extras.softcap or 0.0), int(extras.chunk or 0))
+
+
 def _attention_tc_planned(out, q, k_pool, v_pool, ctx, group: int, scale: float, window: int | None, recorder,
-                          first_row: int = 0, sink: bool = False) -> None:
+                          first_row: int = 0, sink: bool = False, extras: AttentionExtras | None = None) -> None:
     """The tcgen05 attention of the rows from ``first_row`` on, launched so that a CUDA graph can hold it:
     one CTA per SM, the plan of those rows (query tiles, rows, key splits) read from device memory.
     Launches with the same heads and window in one pass share the plan, which ``recorder`` has
@@ -629,12 +635,13 @@ def _attention_tc_planned(out, q, k_pool, v_pool, ctx, group: int, scale: float,
     native.kernel_check(lib.ms_attn_tc_prefill(
         _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(ctx.cu_q) + skip, _ptr(ctx.q_start) + skip, _ptr(ctx.page_indptr[group]) + skip,
         _ptr(ctx.page_indices[group]), 0, t, 0, nq, nkv, k_pool.shape[0], float(scale), int(window or 0), int(sink), k_pool.shape[2],
-        _ptr(device_status(q.device)), 0, 0, _ptr(part), _ptr(queue), _ptr(plan), ctx.stream),
+        _ptr(device_status(q.device)), 0, 0, _ptr(part), _ptr(queue), _ptr(plan), ctx.stream, *_extras_args(extras)),
         lib=lib, errfn="ms_attn_tc_last_error")
 
 
 def attention_tc_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ctx, group: int,
-                         scale: float, window: int | None, first_row: int = 0, sink: bool = False) -> None:
+                         scale: float, window: int | None, first_row: int = 0, sink: bool = False,
+                         extras: AttentionExtras | None = None) -> None:
     """Causal attention of rows [first_row, num_rows) of the step, any number of new tokens each,
     on the tcgen05 tensor cores (``csrc/attention_tc.cu``)."""
     _check_dev(out, q, k_pool, v_pool)
@@ -677,5 +684,6 @@ def attention_tc_prefill(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tenso
     native.kernel_check(lib.ms_attn_tc_prefill(
         _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(ctx.cu_q) + skip, _ptr(ctx.q_start) + skip, _ptr(ctx.page_indptr[group]) + skip,
         _ptr(ctx.page_indices[group]), rows, t, ctx.max_q_len, nq, k_pool.shape[1], k_pool.shape[0], float(scale),
-        int(window or 0), int(sink), k_pool.shape[2], _ptr(device_status(q.device)), splits, min_tiles, _ptr(part), _ptr(queue), None, ctx.stream),
+        int(window or 0), int(sink), k_pool.shape[2], _ptr(device_status(q.device)), splits, min_tiles, _ptr(part), _ptr(queue), None, ctx.stream,
+        *_extras_args(extras)),
         lib=lib, errfn="ms_attn_tc_last_error")

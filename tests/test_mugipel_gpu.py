@@ -172,11 +172,12 @@ def _portions(part, view, x, cuts, page, kv_heads, dtype, full):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads, kv_heads, dim, vdim, rot, page, chunk, softcap", [
-    (4, 2, 32, 16, 8, 8, 12, 6.0), (5, 1, 16, 40, 16, 16, 7, 2.0), (2, 2, 24, 24, 0, 4, None, None), (6, 2, 48, 32, 32, 16, 50, None)])
+    (4, 2, 32, 16, 8, 8, 12, 6.0), (5, 1, 16, 40, 16, 16, 7, 2.0), (2, 2, 24, 24, 0, 4, None, None), (6, 2, 48, 32, 32, 16, 50, None),
+    (4, 2, 128, 128, 64, 16, 100, 5.0), (2, 1, 128, 64, 128, 32, None, 3.0)])  # head size 128: prompts on the tcgen05 kernel
 def test_attention_whole_in_portions_and_decoded(dtype, heads, kv_heads, dim, vdim, rot, page, chunk, softcap):
     att, c = _attention(dtype, heads, kv_heads, dim, vdim, rot, softcap=softcap, chunk=chunk, scaling=rot != 16)
     w = _bind(att, dtype, change=lambda t: t["sink"].mul_(4.0))
-    n = 61
+    n = 61 if dim < 128 else 333
     x = torch.randn(n, HIDDEN, device=DEV).to(dtype) * 2
     ref = _attention_ref(x, w, c)
     pb, ctx = _ctx([(0, n)], page, kv_heads, att.cache_dim, dtype, seed=1)
@@ -207,12 +208,14 @@ def _needle_weights(tensors, heads, kv_heads, dim):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("chunk, n, page", [(16, 41, 8), (20, 75, 16), (512, 700, 16), (2048, 1900, 16)])
-def test_a_key_just_inside_and_just_outside_the_block(dtype, chunk, n, page):
+@pytest.mark.parametrize("chunk, n, page, dim", [(16, 41, 8, 32), (20, 75, 16, 32), (512, 700, 16, 32), (2048, 1900, 16, 32),
+                                                  (100, 777, 16, 128), (300, 1300, 32, 128), (4096, 2100, 16, 128)])
+def test_a_key_just_inside_and_just_outside_the_block(dtype, chunk, n, page, dim):
     """The last query and one earlier token are made so that this pair scores far above everything else. With the
     earlier token at the first position of the last query's block its value must come back; one position before it
-    must not, in a prompt and for a token decoded alone (the long cases cut the decoded token's keys several ways)."""
-    heads, kv_heads, dim, vdim = 4, 2, 32, 32
+    must not, in a prompt and for a token decoded alone (the long cases cut the decoded token's keys several ways;
+    head size 128 runs its prompts on the tcgen05 kernel, the longest one with its keys in several splits)."""
+    heads, kv_heads, vdim = 4, 2, dim
     att, c = _attention(dtype, heads, kv_heads, dim, vdim, 8, scale=1.0, softcap=30.0, chunk=chunk)
     w = _bind(att, dtype, change=lambda t: _needle_weights(t, heads, kv_heads, dim))
     start = ((n - 1) // chunk) * chunk
