@@ -232,6 +232,7 @@ __device__ __forceinline__ void at_rescale(uint32_t t_o, float alpha) {
 // this function and measured slower inside a prompt step (3.60 against 3.53 ms for 2,048 tokens): its
 // 128 live values cost the kernel around the call more than the second read costs here.
 // Returns the sum of the row's exponentials.
+template <bool CAP>
 __device__ __noinline__ float at_softmax_masked(uint32_t t_s, uint32_t t_o, int seen_lo, int seen_hi, float scale_log2,
                                                 float& m_used, float& l_sum, float cap_raw, float cap_c2) {
   float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -243,7 +244,7 @@ __device__ __noinline__ float at_softmax_masked(uint32_t t_s, uint32_t t_o, int 
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       const int off = c * 32 + i;
-      const float sc = cap_c2 > 0.f ? at_cap(v[i], cap_raw, cap_c2) : v[i];
+      const float sc = CAP && cap_c2 > 0.f ? at_cap(v[i], cap_raw, cap_c2) : v[i];
       mx[i & 3] = fmaxf(mx[i & 3], off <= seen_hi && off >= seen_lo ? sc : -INFINITY);
     }
   }
@@ -260,7 +261,7 @@ __device__ __noinline__ float at_softmax_masked(uint32_t t_s, uint32_t t_o, int 
     at_tmem_ld32(t_s + (uint32_t)(c * 32), v);
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
     uint32_t pk[16];
-    if (cap_c2 > 0.f) {
+    if (CAP && cap_c2 > 0.f) {
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = at_cap(v[i], cap_raw, cap_c2);
     }
@@ -377,7 +378,9 @@ __device__ __forceinline__ int at_claim(int* __restrict__ queue, const AtGrid& g
   }
 }
 
-// Persistent: one CTA per SM takes items off a queue until none is left.
+// Persistent: one CTA per SM takes items off a queue until none is left. EXTRAS: the instantiation that takes
+// sink scores, a cap and a block mask (the plain one carries none of their code).
+template <bool EXTRAS>
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
@@ -590,9 +593,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int tok_in_req = m0 + g * tpc + tok;
         const int qpos = start + tok_in_req;
         const int lo_mine = it.lo_g[g], lo_max_mine = it.lo_max[g], q_first_mine = it.q_first[g];
-        const int block_lo = gr.chunk > 0 ? (qpos / gr.chunk) * gr.chunk : 0;
+        const int block_lo = EXTRAS && gr.chunk > 0 ? (qpos / gr.chunk) * gr.chunk : 0;
         // the sink's score in units of log2 (it is neither scaled nor capped)
-        const float sink_l2 = ex.sink_values != nullptr ? ex.sink_values[head0 + hd] * AT_LOG2E : 0.f;
+        const float sink_l2 = EXTRAS && ex.sink_values != nullptr ? ex.sink_values[head0 + hd] * AT_LOG2E : 0.f;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t t_s = tmem + (uint32_t)(g * 128) + lane_base, t_o = tmem + (uint32_t)(256 + g * 128) + lane_base;
         const int n_mine = it.n_tiles[g];
@@ -611,7 +614,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   #pragma unroll
             for (int c = 0; c < 4; ++c) at_tmem_ld32(t_s + (uint32_t)(c * 32), sv[c]);
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-            if (ex.cap_c2 > 0.f) {
+            if (EXTRAS && ex.cap_c2 > 0.f) {
   #pragma unroll
               for (int c = 0; c < 4; ++c)
   #pragma unroll
@@ -648,7 +651,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // that this row sees are those at offsets [seen_lo, seen_hi]
             const int seen_hi = qpos - key0;
             const int seen_lo = max(max(lo_mine, block_lo), window > 0 ? qpos - window + 1 : 0) - key0;
-            part[0] = at_softmax_masked(t_s, t_o, seen_lo, seen_hi, scale_log2, m_used, l_sum, ex.cap_raw, ex.cap_c2);
+            part[0] = at_softmax_masked<EXTRAS>(t_s, t_o, seen_lo, seen_hi, scale_log2, m_used, l_sum, ex.cap_raw, ex.cap_c2);
           }
           l_sum += (part[0] + part[1]) + (part[2] + part[3]);
           const int valid_keys = kv_len - key0;
@@ -949,7 +952,8 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
   constexpr size_t smem_bytes = AtSmem::total + 1024;
   static bool configured = false;
   if (!configured) {
-    MS_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+    MS_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+    MS_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
     configured = true;
   }
   static int sm_count = 0;
@@ -963,10 +967,17 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
   MS_CHECK_ARG(total < (1LL << 30), "attention_tc: %lld work items are too many for one launch", total);
   // one CTA fills an SM (192 KB of shared memory, all of tensor memory) and takes items until none is left
   const unsigned grid = (unsigned)(plan == nullptr && total < sm_count ? total : sm_count);
-  MS_LAUNCH(attn_prefill_tc_kernel, grid, AT_THREADS, smem_bytes, stream, map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q,
-            q_start, page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, sink, page_shift, gr, status,
-            partials, reinterpret_cast<float2*>(partials + (total / gr.splits) * 2 * gr.splits * (AT_ROWS * AT_D)), queue,
-            queue + 2, plan, ex);
+  if (sink_values != nullptr || softcap > 0.f || chunk > 0) {
+    MS_LAUNCH(attn_prefill_tc_kernel<true>, grid, AT_THREADS, smem_bytes, stream, map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q,
+              q_start, page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, sink, page_shift, gr, status,
+              partials, reinterpret_cast<float2*>(partials + (total / gr.splits) * 2 * gr.splits * (AT_ROWS * AT_D)), queue,
+              queue + 2, plan, ex);
+  } else {
+    MS_LAUNCH(attn_prefill_tc_kernel<false>, grid, AT_THREADS, smem_bytes, stream, map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q,
+              q_start, page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, sink, page_shift, gr, status,
+              partials, reinterpret_cast<float2*>(partials + (total / gr.splits) * 2 * gr.splits * (AT_ROWS * AT_D)), queue,
+              queue + 2, plan, ex);
+  }
   return 0;
 }
 
