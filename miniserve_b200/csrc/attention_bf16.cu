@@ -106,8 +106,12 @@ struct AttnExtras {
   int chunk;                 // 0: no block mask
 };
 
+// tanh(y) = 1 - 2 / (1 + 2^(2 y log2 e)): two fast special-function operations, absolute error about 1e-6 (times the
+// cap, far below the bfloat16 rounding of the probabilities)
 __device__ __forceinline__ float shaped_score(float s, float scale_log2, const AttnExtras& ex) {
-  return ex.cap_inv > 0.f ? ex.cap_log2 * tanhf(s * ex.cap_inv) : s * scale_log2;
+  if (ex.cap_inv <= 0.f) return s * scale_log2;
+  const float e = exp2f(s * ex.cap_inv * (2.f * LOG2E));
+  return ex.cap_log2 * (1.f - __fdividef(2.f, 1.f + e));
 }
 // the sink's term of the denominator, in units of 2^-m
 __device__ __forceinline__ float sink_term(int sink, const AttnExtras& ex, int head, float m) {

@@ -9,6 +9,7 @@
 //   * relu(x)^2 written at a column offset of a wider row;
 //   * a sigmoid gate per (token, channel) on attention's output, cut to the value size and written at a
 //     column offset of a wider row;
+//   * both of these in one launch, for a block whose mixer and feed-forward share the row;
 //   * the cos/sin table of a step with a factor on both (rotations whose frequencies were rescaled for
 //     longer contexts carry such a factor);
 //   * the latent of latent attention: a column range of a projection, RMS-normed with a float32
@@ -183,6 +184,58 @@ __global__ void channel_gate_bf16x8_kernel(__nv_bfloat16* __restrict__ out, int 
   *reinterpret_cast<uint4*>(out + t * ld_out + (size_t)h * dv8 * 8 + 8 * c) = float_to_bf16x8(a);
 }
 
+// Both halves of a joint features row in one launch: columns [0, nq * dv) = sigmoid(gate) * attention (as
+// channel_gate), columns [nq * dv, nq * dv + inter) = relu(up)^2 (as relu_squared).
+template <typename T>
+__global__ void gate_relu_squared_kernel(T* __restrict__ out, int ld_out, const T* __restrict__ attn, const T* __restrict__ gate,
+                                         int ld_gate, const T* __restrict__ up, int ld_up, long long items, int nq, int d_pad, int dv,
+                                         int inter) {
+  pdl_prologue();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= items) return;
+  const int fa = nq * dv, width = fa + inter;
+  const long long t = idx / width;
+  const int col = (int)(idx - t * width);
+  float y;
+  if (col < fa) {
+    const int h = col / dv, c = col - h * dv;
+    y = Elem<T>::load(attn + (t * nq + h) * d_pad + c) / (1.0f + expf(-Elem<T>::load(gate + t * ld_gate + col)));
+  } else {
+    const float z = fmaxf(Elem<T>::load(up + t * ld_up + (col - fa)), 0.f);
+    y = z * z;
+  }
+  Elem<T>::store(out + t * ld_out + col, y);
+}
+
+__global__ void gate_relu_squared_bf16x8_kernel(__nv_bfloat16* __restrict__ out, int ld_out, const __nv_bfloat16* __restrict__ attn,
+                                                const __nv_bfloat16* __restrict__ gate, int ld_gate,
+                                                const __nv_bfloat16* __restrict__ up, int ld_up, long long items8, int nq, int d_pad,
+                                                int dv, int inter) {
+  pdl_prologue();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= items8) return;
+  const int fa = nq * dv, width8 = (fa + inter) >> 3;
+  const long long t = idx / width8;
+  const int col = (int)(idx - t * width8) * 8;
+  float a[8];
+  if (col < fa) {
+    const int h = col / dv, c = col - h * dv;
+    float g[8];
+    bf16x8_to_float(*reinterpret_cast<const uint4*>(attn + (t * nq + h) * d_pad + c), a);
+    bf16x8_to_float(*reinterpret_cast<const uint4*>(gate + t * ld_gate + col), g);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = a[e] / (1.0f + expf(-g[e]));
+  } else {
+    bf16x8_to_float(*reinterpret_cast<const uint4*>(up + t * ld_up + (col - fa)), a);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float z = fmaxf(a[e], 0.f);
+      a[e] = z * z;
+    }
+  }
+  *reinterpret_cast<uint4*>(out + t * ld_out + col) = float_to_bf16x8(a);
+}
+
 __global__ void rope_table_scaled_kernel(float* __restrict__ table, const int* __restrict__ positions,
                                          const float* __restrict__ inv_freq, float factor, int num_tokens, int rot) {
   pdl_prologue();
@@ -330,6 +383,28 @@ MS_EXPORT int ms_channel_gate(void* out, int ld_out, const void* attn, const voi
   else
     MS_LAUNCH(channel_gate_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, ld_out, (const __nv_bfloat16*)attn,
               (const __nv_bfloat16*)gate, ld_gate, items, nq, d_pad, dv, scale);
+  return 0;
+}
+
+MS_EXPORT int ms_gate_relu_squared(void* out, int ld_out, const void* attn, const void* gate, int ld_gate, const void* up, int ld_up,
+                                   int num_tokens, int nq, int d_pad, int dv, int inter, int dtype, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  MS_CHECK_ARG(nq > 0 && dv > 0 && dv <= d_pad && inter > 0, "gate_relu_squared: bad sizes nq=%d dv=%d D=%d inter=%d", nq, dv, d_pad, inter);
+  const long long items = (long long)num_tokens * ((long long)nq * dv + inter);
+  const bool aligned = (uintptr_t)out % 16 == 0 && (uintptr_t)attn % 16 == 0 && (uintptr_t)gate % 16 == 0 && (uintptr_t)up % 16 == 0;
+  if (dtype == MS_BF16 && dv % 8 == 0 && d_pad % 8 == 0 && inter % 8 == 0 && ld_out % 8 == 0 && ld_gate % 8 == 0 && ld_up % 8 == 0 && aligned) {
+    MS_LAUNCH(gate_relu_squared_bf16x8_kernel, (unsigned)((items / 8 + 255) / 256), 256, 0, stream, (__nv_bfloat16*)out, ld_out,
+              (const __nv_bfloat16*)attn, (const __nv_bfloat16*)gate, ld_gate, (const __nv_bfloat16*)up, ld_up, items / 8, nq, d_pad, dv,
+              inter);
+    return 0;
+  }
+  const unsigned blocks = (unsigned)((items + 255) / 256);
+  if (dtype == MS_F32)
+    MS_LAUNCH(gate_relu_squared_kernel<float>, blocks, 256, 0, stream, (float*)out, ld_out, (const float*)attn, (const float*)gate,
+              ld_gate, (const float*)up, ld_up, items, nq, d_pad, dv, inter);
+  else
+    MS_LAUNCH(gate_relu_squared_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, ld_out, (const __nv_bfloat16*)attn,
+              (const __nv_bfloat16*)gate, ld_gate, (const __nv_bfloat16*)up, ld_up, items, nq, d_pad, dv, inter);
   return 0;
 }
 

@@ -112,8 +112,10 @@ __global__ void head_gate_bf16x8_kernel(__nv_bfloat16* __restrict__ out, int ld_
   }
 }
 
-// bfloat16, adjacent rotation pairs, sizes that are multiples of 8, rows on 16 bytes: a lane holds eight
-// consecutive channels (four rotation pairs), so the rotation needs no exchange; one warp per (token, head).
+// bfloat16, sizes that are multiples of 8, rows on 16 bytes: a lane holds eight consecutive channels; one warp per
+// (token, head). ADJACENT: these are four rotation pairs, so the rotation needs no exchange. Otherwise channel i
+// turns with channel i + rot / 2 (rot a multiple of 16): the lane loads its partners' eight channels as well.
+template <bool ADJACENT>
 __global__ void qkv_prepare_bf16x8_kernel(
     __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool,
     const __nv_bfloat16* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ q_norm_w,
@@ -183,15 +185,33 @@ __global__ void qkv_prepare_bf16x8_kernel(
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[e] = (v[e] * inv) * nw[c + e];
       }
+      if (ADJACENT) {
 #pragma unroll
-      for (int e = 0; e < 8; e += 2) {
-        const int j = (c + e) >> 1;
-        if (j < half) {
-          const float cs = cos_sin[(size_t)t * rot + j], sn = cos_sin[(size_t)t * rot + half + j];
-          const float a = v[e], b = v[e + 1];
-          v[e] = a * cs - b * sn;
-          v[e + 1] = b * cs + a * sn;
+        for (int e = 0; e < 8; e += 2) {
+          const int j = (c + e) >> 1;
+          if (j < half) {
+            const float cs = cos_sin[(size_t)t * rot + j], sn = cos_sin[(size_t)t * rot + half + j];
+            const float a = v[e], b = v[e + 1];
+            v[e] = a * cs - b * sn;
+            v[e + 1] = b * cs + a * sn;
+          }
         }
+      } else if (c < rot) {
+        const bool first = c < half;  // this chunk holds the pairs' first members (u), its partner chunk the second (v)
+        const int pc = first ? c + half : c - half, j0 = first ? c : c - half;
+        float p[8];
+        bf16x8_to_float(*reinterpret_cast<const uint4*>(src + pc), p);
+        if (nw) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) p[e] = (p[e] * inv) * nw[pc + e];
+        }
+        const float4 c0 = *reinterpret_cast<const float4*>(cos_sin + (size_t)t * rot + j0);
+        const float4 c1 = *reinterpret_cast<const float4*>(cos_sin + (size_t)t * rot + j0 + 4);
+        const float4 s0 = *reinterpret_cast<const float4*>(cos_sin + (size_t)t * rot + half + j0);
+        const float4 s1 = *reinterpret_cast<const float4*>(cos_sin + (size_t)t * rot + half + j0 + 4);
+        const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w}, sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = first ? v[e] * cs[e] - p[e] * sn[e] : v[e] * cs[e] + p[e] * sn[e];
       }
     }
     *reinterpret_cast<uint4*>(dst + c) = float_to_bf16x8(v);
@@ -369,12 +389,17 @@ MS_EXPORT int ms_qkv_prepare(void* q_out, void* k_pool, void* v_pool, const void
   const long long items = (long long)num_tokens * (nq + 2 * nkv);
   const int warps = 8;
   const unsigned blocks = (unsigned)((items + warps - 1) / warps);
-  if (dtype == MS_BF16 && (adjacent || rot == 0) && dk % 8 == 0 && dv % 8 == 0 && d_pad % 8 == 0 && ld % 8 == 0 && q_off % 8 == 0 &&
+  if (dtype == MS_BF16 && (adjacent || rot % 16 == 0) && dk % 8 == 0 && dv % 8 == 0 && d_pad % 8 == 0 && ld % 8 == 0 && q_off % 8 == 0 &&
       k_off % 8 == 0 && v_off % 8 == 0 && (uintptr_t)proj % 16 == 0 && (uintptr_t)q_out % 16 == 0 && (uintptr_t)k_pool % 16 == 0 &&
       (uintptr_t)v_pool % 16 == 0) {
-    MS_LAUNCH(qkv_prepare_bf16x8_kernel, blocks, warps * 32, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
-              (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)proj, ld, q_off, k_off, v_off, q_norm_w, k_norm_w, cos_sin, positions,
-              row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, dk, dv, d_pad, rot, eps, page_shift, num_pages, status);
+    if (adjacent || rot == 0)
+      MS_LAUNCH(qkv_prepare_bf16x8_kernel<true>, blocks, warps * 32, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
+                (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)proj, ld, q_off, k_off, v_off, q_norm_w, k_norm_w, cos_sin, positions,
+                row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, dk, dv, d_pad, rot, eps, page_shift, num_pages, status);
+    else  // (the table's rows are rot floats wide: 16-byte loads of eight cosines need rot / 2 a multiple of 8, which rot % 16 gives)
+      MS_LAUNCH(qkv_prepare_bf16x8_kernel<false>, blocks, warps * 32, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
+                (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)proj, ld, q_off, k_off, v_off, q_norm_w, k_norm_w, cos_sin, positions,
+                row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, dk, dv, d_pad, rot, eps, page_shift, num_pages, status);
     return 0;
   }
   if (dtype == MS_F32)

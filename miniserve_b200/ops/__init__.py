@@ -14,7 +14,7 @@ import torch
 
 from . import blas, native
 from .mixers import (add_dyt, add_rmsnorm_scaled, add_row_vector, axpby, channel_gate, conv_silu_unit,  # noqa: F401
-                     conv_state_update, decay_scan, gelu_tanh, head_gate, head_norm_gate, latent_prepare, qkv_prepare,
+                     conv_state_update, decay_scan, gate_relu_squared, gelu_tanh, head_gate, head_norm_gate, latent_prepare, qkv_prepare,
                      relu_squared, rope_table_scaled, scale_, stream_concat)
 from .native import NativeError, OutOfBlocks
 

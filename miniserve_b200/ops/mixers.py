@@ -263,6 +263,18 @@ def channel_gate(out: torch.Tensor, attn: torch.Tensor, gate: torch.Tensor, valu
         _ptr(out), _rows(out), _ptr(attn), _ptr(gate), _rows(gate), t, nq, d, value_dim, float(scale), _dt(attn.dtype), _stream(stream)))
 
 
+def gate_relu_squared(out: torch.Tensor, attn: torch.Tensor, gate: torch.Tensor, value_dim: int, up: torch.Tensor, stream=None) -> None:
+    """One launch for a row that holds a mixer's and a feed-forward's features side by side: out[t, :H*dv] as
+    ``channel_gate`` (scale 1), out[t, H*dv:H*dv+I] = max(up[t], 0)^2. ``out``, ``gate`` and ``up`` are 2-d views of wider rows."""
+    t, nq, d = attn.shape
+    inter = up.shape[1]
+    assert attn.is_contiguous() and out.shape == (t, nq * value_dim + inter) and out.dtype == attn.dtype == gate.dtype == up.dtype
+    assert gate.shape == (t, nq * value_dim) and up.shape[0] == t
+    native.mixers_check(native.mixers().ms_gate_relu_squared(
+        _ptr(out), _rows(out), _ptr(attn), _ptr(gate), _rows(gate), _ptr(up), _rows(up), t, nq, d, value_dim, inter, _dt(attn.dtype),
+        _stream(stream)))
+
+
 def rope_table_scaled(positions: torch.Tensor, inv_freq: torch.Tensor, factor: float, num_tokens: int, rotary_dim: int,
                       stream=None) -> torch.Tensor:
     """float32 [T, rotary_dim]: factor * cos, then factor * sin, of position * inv_freq for every token of a step."""

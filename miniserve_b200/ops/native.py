@@ -134,6 +134,7 @@ def mixers():
     _declare(lib, "ms_add_row_vector", [_p, _p, _i, _i, _p])
     _declare(lib, "ms_relu_squared", [_p, _i, _p, _i, _i, _i, _i, _p])
     _declare(lib, "ms_channel_gate", [_p, _i, _p, _p, _i, _i, _i, _i, _i, _f, _i, _p])
+    _declare(lib, "ms_gate_relu_squared", [_p, _i, _p, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _p])
     _declare(lib, "ms_rope_table_scaled", [_p, _p, _p, _f, _i, _i, _p])
     _declare(lib, "ms_latent_prepare", [_p, _p, _i, _i, _p, _f, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _p])
     return lib

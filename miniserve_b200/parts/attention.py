@@ -39,6 +39,7 @@ class GQAttention(Part):
     ``out_gate`` = ``channel_sigmoid`` (attention's output is multiplied element by element by sigmoid(W_g x),
     W_g as wide as the concatenated heads). All of them take the general path."""
     shape_static = True
+    input_weight = "w_qkv"  # the attribute that holds the input product's (stacked) matrix; its first ``input_rows`` rows are real
     NAMES = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight", q_norm="q_norm.weight",
                  k_norm="k_norm.weight", gate="g_proj.weight", sink="sink")
 
@@ -129,6 +130,7 @@ class GQAttention(Part):
         n = self.names
         if self.owns_cache:
             self.w_qkv = self.joined(tensors, *self._stack())
+            self.input_rows = self.w_qkv.shape[0]  # rows of the input product that are this mixer's (before any padding)
             if self.general and self.w_qkv.shape[0] % 8:
                 # rows of the product's output start on 16 bytes: a few zero rows at the end
                 pad = torch.zeros((-self.w_qkv.shape[0] % 8, self.hidden), dtype=self.w_qkv.dtype, device=self.w_qkv.device)
@@ -149,13 +151,18 @@ class GQAttention(Part):
         need = self.cache_need()
         return need.window if need is not None else (int(self.window) if self.window else None)
 
-    def features(self, x: torch.Tensor, ctx, cache, out: torch.Tensor, scale: float = 1.0) -> None:
+    def features(self, x: torch.Tensor, ctx, cache, out: torch.Tensor | None, scale: float = 1.0, proj: torch.Tensor | None = None,
+                 defer_gate: bool = False):
         """The general path up to the output projection's input: ``out`` [T, heads * value_dim] (a view
-        whose rows may be part of wider ones) = scale * gate * attention."""
+        whose rows may be part of wider ones) = scale * gate * attention. ``proj``: the q|k|v|gate projection if
+        the caller made it already (columns of a wider product, in this mixer's order). ``defer_gate`` (per-channel
+        gates only): nothing is written; attention's output [T, heads, D] and the gate's columns are returned for a
+        caller that applies the gate together with something else."""
         t = x.shape[0]
-        dt, dev = self.env.dtype, self.w_qkv.device
+        dt, dev = self.env.dtype, x.device
         nq, nkv, dk, dv, dc = self.heads, self.kv_heads, self.head_dim, self.value_dim, self.cache_dim
-        proj = ops.linear(x, self.w_qkv, stream=ctx.stream, out=ctx.buffer("attn.qkv", (t, self.w_qkv.shape[0]), dt, dev))
+        if proj is None:
+            proj = ops.linear(x, self.w_qkv, stream=ctx.stream, out=ctx.buffer("attn.qkv", (t, self.w_qkv.shape[0]), dt, dev))
         at_k, at_v, at_g = nq * dk, (nq + nkv) * dk, (nq + nkv) * dk + nkv * dv
         q = ctx.buffer("attn.q", (t, nq, dc), dt, dev)
         _, rotary_dim = self.position.kernel_table()
@@ -166,6 +173,8 @@ class GQAttention(Part):
         att = ctx.buffer("attn.out", (t, nq, dc), dt, dev)
         ops.attention(att, q, cache.k, cache.v, ctx, cache.group, self.scale, self.reach, self.sink, extras=self.extras)
         if self.out_gate == "channel_sigmoid":
+            if defer_gate:
+                return att, proj[:, at_g:at_g + nq * dv]
             ops.channel_gate(out, att, proj[:, at_g:at_g + nq * dv], dv, scale, stream=ctx.stream)
             return
         gate = proj[:, at_g:at_g + nq] if self.out_gate else None
@@ -174,7 +183,7 @@ class GQAttention(Part):
     def forward(self, x: torch.Tensor, ctx, cache):
         """Returns the mixer's addend to the residual stream: a tensor [T, hidden]."""
         t = x.shape[0]
-        dt, dev = self.env.dtype, self.w_qkv.device
+        dt, dev = self.env.dtype, x.device
         if self.general:
             feat = ctx.buffer("attn.feat", (t, self.feature_width), dt, dev)
             self.features(x, ctx, cache, feat)

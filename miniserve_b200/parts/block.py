@@ -59,6 +59,11 @@ class ParallelResidualBlock(Part):
     they write their features side by side into one row and ONE product with the two output matrices joined along
     their inputs makes the sum; otherwise the two outputs are added. The sum is handed on as the pending addend
     with ``residual_mult`` as its factor, so the multiplication and the add happen in float32 inside the next norm.
+    The input side is joined likewise when the mixer says which tensor its input product uses (``input_weight``,
+    ``input_rows``) and gates per channel, and the feed-forward's activation is squared ReLU: ONE product with the
+    mixer's input matrices and the up projection stacked makes q, k, v, gate and up (or q, latent, gate and up),
+    and one kernel applies the gate and the activation into the joint row. The parts' own copies of the joined
+    matrices are dropped.
     Parameters: ``names`` (mixer / feed_forward / norm1 -> tensor-name prefixes), ``residual_mult``. A layer
     without a feed-forward adds the mixer's output alone."""
     shape_static = True
@@ -78,6 +83,8 @@ class ParallelResidualBlock(Part):
         if self.joint and getattr(self.mixer, "general", True) is False:
             self.joint = False  # an attention on its own fused path has no such stop
         self.w_out = None
+        self.w_in = None
+        self.joint_in = False
 
     def sub_parts(self):
         out = {self.names["mixer"]: self.mixer, self.names["norm1"]: self.norm1}
@@ -92,6 +99,20 @@ class ParallelResidualBlock(Part):
             if w.shape[1] % 8:  # the product wants rows of whole 16 bytes: zero columns, which meet zero features
                 w = torch.cat((w, torch.zeros((w.shape[0], -w.shape[1] % 8), dtype=w.dtype, device=w.device)), dim=1)
             self.w_out = w.contiguous()
+            mixer, ff = self.mixer, self.feed_forward
+            name = getattr(mixer, "input_weight", None)
+            self.joint_in = bool(name and getattr(mixer, "out_gate", "channel_sigmoid") == "channel_sigmoid"
+                                 and getattr(ff, "activation", None) == "relu_squared")
+            if self.joint_in:
+                own = getattr(mixer, name)[:mixer.input_rows]
+                w = torch.cat([own, ff.w_up], dim=0)  # [mixer's input rows + intermediate, hidden]
+                if w.shape[0] % 8:  # rows of the product's output start on 16 bytes: a few zero rows at the end
+                    w = torch.cat((w, torch.zeros((-w.shape[0] % 8, w.shape[1]), dtype=w.dtype, device=w.device)), dim=0)
+                self.w_in = w.contiguous()
+                setattr(mixer, name, None)  # the joined matrices live in this block now
+                ff.w_up = None
+            mixer.w_o = None
+            ff.w_down = None
 
     def forward(self, stream: ResidualStream, ctx, cache) -> ResidualStream:
         total = stream.total
@@ -102,8 +123,14 @@ class ParallelResidualBlock(Part):
         if self.joint:
             fa, fb = self.mixer.feature_width, self.feed_forward.feature_width
             feat = ctx.buffer("block.feat", (t, self.w_out.shape[1]), dt, dev)
-            self.mixer.features(x, ctx, cache, feat[:, :fa])
-            self.feed_forward.features(x, ctx, feat[:, fa:fa + fb])
+            if self.joint_in:
+                rows = self.mixer.input_rows
+                proj = ops.linear(x, self.w_in, stream=ctx.stream, out=ctx.buffer("block.in", (t, self.w_in.shape[0]), dt, dev))
+                vals, gate = self.mixer.features(x, ctx, cache, None, proj=proj[:, :rows], defer_gate=True)
+                ops.gate_relu_squared(feat[:, :fa + fb], vals, gate, self.mixer.value_dim, proj[:, rows:rows + fb], stream=ctx.stream)
+            else:
+                self.mixer.features(x, ctx, cache, feat[:, :fa])
+                self.feed_forward.features(x, ctx, feat[:, fa:fa + fb])
             if fa + fb < feat.shape[1]:
                 feat[:, fa + fb:].zero_()
             y = ops.linear(feat, self.w_out, stream=ctx.stream, out=ctx.buffer("block.out", (t, self.w_out.shape[0]), dt, dev))

@@ -25,6 +25,7 @@ class LatentAttention(Part):
     norm, up_k, up_v, gate, o -> tensor names). ``features`` stops before the output projection."""
     shape_static = True
     general = True
+    input_weight = "w_in"  # the attribute that holds the input product's (stacked) matrix; its first ``input_rows`` rows are real
     NAMES = dict(q="q_proj.weight", down="kv_down_proj.weight", norm="kv_norm.weight", up_k="k_up_proj.weight",
                  up_v="v_up_proj.weight", gate="g_proj.weight", o="o_proj.weight")
     MAX_LATENT = 256  # the largest head size the attention kernels take
@@ -68,6 +69,7 @@ class LatentAttention(Part):
     def bind(self, tensors):
         n, h, r, rc = self.names, self.heads, self.latent, self.cache_dim
         w_in = self.joined(tensors, *self._stack())
+        self.input_rows = w_in.shape[0]  # rows of the input product that are this mixer's (before any padding)
         if w_in.shape[0] % 8:  # rows of the product's output start on 16 bytes: a few zero rows at the end
             w_in = torch.cat((w_in, torch.zeros((-w_in.shape[0] % 8, self.hidden), dtype=w_in.dtype, device=w_in.device)), dim=0)
         self.w_in = w_in.contiguous()
@@ -82,12 +84,17 @@ class LatentAttention(Part):
         self.w_uv[:, :, :r] = uv
         self.w_o = tensors[n["o"]].contiguous()
 
-    def features(self, x: torch.Tensor, ctx, cache, out: torch.Tensor, scale: float = 1.0) -> None:
-        """``out`` [T, heads * value_dim] (a view whose rows may be part of wider ones) = scale * gate * attention."""
+    def features(self, x: torch.Tensor, ctx, cache, out: torch.Tensor | None, scale: float = 1.0, proj: torch.Tensor | None = None,
+                 defer_gate: bool = False):
+        """``out`` [T, heads * value_dim] (a view whose rows may be part of wider ones) = scale * gate * attention.
+        ``proj``: the q|latent|gate projection if the caller made it already (columns of a wider product).
+        ``defer_gate``: nothing is written; the heads' values [T, heads, value_dim] and the gate's columns are
+        returned for a caller that applies the gate together with something else."""
         t = x.shape[0]
-        dt, dev = self.env.dtype, self.w_in.device
+        dt, dev = self.env.dtype, x.device
         h, dk, dv, r, rc = self.heads, self.head_dim, self.value_dim, self.latent, self.cache_dim
-        proj = ops.linear(x, self.w_in, stream=ctx.stream, out=ctx.buffer("lat.in", (t, self.w_in.shape[0]), dt, dev))
+        if proj is None:
+            proj = ops.linear(x, self.w_in, stream=ctx.stream, out=ctx.buffer("lat.in", (t, self.w_in.shape[0]), dt, dev))
         at_c, at_g = h * dk, h * dk + r
         ops.latent_prepare(cache.k, proj[:, at_c:at_g], self.w_norm, self.eps, ctx.positions, ctx.row_of_token,
                            ctx.page_indptr[cache.group], ctx.page_indices[cache.group], cache.page_size, ctx.status, stream=ctx.stream)
@@ -97,11 +104,13 @@ class LatentAttention(Part):
         ops.attention(att, q, cache.k, cache.v, ctx, cache.group, self.scale, None, False)
         val = ctx.buffer("lat.val", (t, h, dv), dt, dev)
         ops.linear_heads(att, self.w_uv, val, stream=ctx.stream)
+        if defer_gate:
+            return val, proj[:, at_g:at_g + h * dv]
         ops.channel_gate(out, val, proj[:, at_g:at_g + h * dv], dv, scale, stream=ctx.stream)
 
     def forward(self, x: torch.Tensor, ctx, cache):
         t = x.shape[0]
-        dt, dev = self.env.dtype, self.w_in.device
+        dt, dev = self.env.dtype, x.device
         feat = ctx.buffer("lat.feat", (t, self.feature_width), dt, dev)
         self.features(x, ctx, cache, feat)
         return ops.linear(feat, self.w_o, stream=ctx.stream, out=ctx.buffer("lat.proj", (t, self.w_o.shape[0]), dt, dev))

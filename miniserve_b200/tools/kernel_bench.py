@@ -6,6 +6,9 @@ summaries under ``profiles/`` were measured and captured with.
     python -m miniserve_b200.tools.kernel_bench skinny --m 8 --n 4096 --k 1024
     python -m miniserve_b200.tools.kernel_bench sample --batch 8 --top-p 0.9
     python -m miniserve_b200.tools.kernel_bench decay_scan --tokens 2048 --heads 8 --key-dim 64 --value-dim 128 [--delta]
+    python -m miniserve_b200.tools.kernel_bench attn_prefill --tokens 2048 --softcap 50 --chunk 1024 --learned-sink
+    python -m miniserve_b200.tools.kernel_bench add_rmsnorm --m 2048 --n 1024 --offset
+    python -m miniserve_b200.tools.kernel_bench pointwise --op channel_gate --tokens 2048 --heads 16 --head-dim 128
 
 Each case rotates over enough copies of its inputs to exceed the L2 cache, captures one pass over
 all copies in a CUDA graph, and reports the time per launch with the bytes or flops it implies.
@@ -87,7 +90,7 @@ def _time(calls, copies, launches):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
-    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "skinny", "add_rmsnorm", "gemm", "gate_up", "sample", "decay_scan"])
+    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "skinny", "add_rmsnorm", "gemm", "gate_up", "sample", "decay_scan", "pointwise"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -107,6 +110,12 @@ def main(argv=None) -> int:
     ap.add_argument("--key-dim", type=int, default=64, help="decay_scan: key channels of a head")
     ap.add_argument("--value-dim", type=int, default=128, help="decay_scan: value channels of a head")
     ap.add_argument("--delta", action="store_true", help="decay_scan: the delta rule instead of the decay rule")
+    ap.add_argument("--softcap", type=float, default=0.0, help="attn_*: scores capped at this (0: none)")
+    ap.add_argument("--chunk", type=int, default=0, help="attn_*: a query sees only its own block of this many positions (0: all)")
+    ap.add_argument("--learned-sink", action="store_true", help="attn_*: a sink with a score per head")
+    ap.add_argument("--offset", action="store_true", help="add_rmsnorm: the kernel with a float32 weight stored around zero and a factor on the addend")
+    ap.add_argument("--op", choices=["channel_gate", "head_gate", "relu_squared", "gelu_tanh", "latent_prepare", "qkv_prepare"],
+                    default="channel_gate", help="pointwise: which kernel (--tokens rows; --heads x --head-dim, or --n, columns)")
     ap.add_argument("--launches", type=int, default=0, help="run this many plain launches and report nothing")
     args = ap.parse_args(argv)
 
@@ -122,18 +131,24 @@ def main(argv=None) -> int:
             work = dict(bytes=byts)
         else:
             rows = [(args.prefix, args.tokens)]  # a portion of a prompt behind `prefix` cached tokens
-            flops = 4.0 * nq * d * (args.tokens * (args.tokens + 1) / 2 + args.tokens * args.prefix)
+            pairs = args.tokens * (args.tokens + 1) / 2 + args.tokens * args.prefix
+            if args.chunk:
+                pairs = sum(p % args.chunk + 1 for p in range(args.prefix, args.prefix + args.tokens))
+            flops = 4.0 * nq * d * pairs
             byts = (args.prefix + args.tokens) * nkv * d * 4
             work = dict(flops=flops)
         copies = max(2, int(L2_BYTES // byts) + 1)
         sets = [_paged(rows, args.page_size, nkv, d, i, dev) for i in range(copies)]
         q = torch.randn(sum(n for _, n in rows), nq, d, device=dev).bfloat16()
         o = torch.empty_like(q)
+        if args.kernel == "attn_decode" and args.chunk:
+            work = dict(bytes=args.batch * (args.context % args.chunk + 1) * nkv * d * 2 * 2)
+        extras = ops.AttentionExtras(torch.randn(nq, device=dev) if args.learned_sink else None, args.softcap, args.chunk)
 
         def calls(i, stream):
             k, v, ctx = sets[i]
             ctx.stream = stream
-            ops.attention(o, q, k, v, ctx, 0, d ** -0.5, None)
+            ops.attention(o, q, k, v, ctx, 0, d ** -0.5, args.chunk or None, extras=extras)
     elif args.kernel in ("gemm", "gate_up"):
         # gemm: x [m, k] times w [n, k]^T; gate_up: silu(x Wg^T) * (x Wu^T) with the stacked weight [2 n, k]
         ops.TC_GEMM = {"auto": "auto", "tcgen05": "1", "library": "0"}[args.gemm]
@@ -189,8 +204,50 @@ def main(argv=None) -> int:
         w = torch.ones(h, device=dev).bfloat16()
         o = torch.empty(args.m, h, device=dev, dtype=torch.bfloat16)
 
+        wf = torch.zeros(h, device=dev)
+
         def calls(i, stream):
-            ops.add_rmsnorm(o, res, delta, w, 1e-6, stream=stream)
+            if args.offset:
+                ops.add_rmsnorm_scaled(o, res, delta, 0.5, wf, 1.0, 1e-6, stream=stream)
+            else:
+                ops.add_rmsnorm(o, res, delta, w, 1e-6, stream=stream)
+    elif args.kernel == "pointwise":
+        t, nq, d = args.tokens, args.heads, args.head_dim
+        width = nq * d
+        bf = dict(device=dev, dtype=torch.bfloat16)
+        per_set = t * width * 2 * 6
+        copies = max(2, int(L2_BYTES // per_set) + 1)
+        # a projection's rows (operands are column ranges of it), attention's output, and the row that features are written into
+        sets = [(torch.randn(t, nq, d, **bf), torch.randn(t, 3 * width + 8, **bf), torch.empty(t, 2 * width, **bf)) for _ in range(copies)]
+        pool, _, pctx = _paged([(0, t)], args.page_size, 1, d, 0, dev)
+        kpool, vpool, kctx = _paged([(0, t)], args.page_size, nq, d, 1, dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+        positions, row_of = torch.arange(t, **i32), torch.zeros(t, **i32)
+        status = torch.zeros(1, **i32)
+        wn = torch.ones(d, device=dev)
+        table = torch.randn(t, d, device=dev)
+        qo = torch.empty(t, nq, d, **bf)
+        byts = {"channel_gate": 3 * t * width * 2, "head_gate": 2 * t * width * 2, "relu_squared": 2 * t * width * 2,
+                "gelu_tanh": 2 * t * width * 2, "latent_prepare": 2 * t * d * 2, "qkv_prepare": 2 * 3 * t * width * 2}[args.op]
+        work = dict(bytes=byts)
+
+        def calls(i, stream):
+            att, wide, feat = sets[i]
+            if args.op == "channel_gate":
+                ops.channel_gate(feat[:, :width], att, wide[:, width:2 * width], d, 1.0, stream=stream)
+            elif args.op == "head_gate":
+                ops.head_gate(feat[:, :width], att, wide[:, width:width + nq], d, 1.0, stream=stream)
+            elif args.op == "relu_squared":
+                ops.relu_squared(feat[:, width:], wide[:, :width], stream=stream)
+            elif args.op == "gelu_tanh":
+                ops.gelu_tanh(qo, att, stream=stream)
+            elif args.op == "latent_prepare":
+                ops.latent_prepare(pool, wide[:, width:width + d], wn, 1e-6, positions, row_of, pctx.page_indptr[0], pctx.page_indices[0],
+                                   args.page_size, status, stream=stream)
+            else:
+                ops.qkv_prepare(qo, kpool, vpool, wide[:, :width], wide[:, width:2 * width], wide[:, 2 * width:3 * width], None, None, table,
+                                d, False, 1e-6, positions, row_of, kctx.page_indptr[0], kctx.page_indices[0], args.page_size, status,
+                                stream=stream)
     else:
         # the linear-attention recurrence: `batch` requests of `tokens` tokens each (1: a decode step), from zero state
         t, hh, dk, dv, rows = args.tokens * args.batch, args.heads, args.key_dim, args.value_dim, args.batch
