@@ -354,16 +354,16 @@ def fekulix_config(width: int, ff: int, runs: int, vocab: int, heads: int, kv_he
 
 def mugipel_config(width: int, ff: int, runs: int, vocab: int, heads: int, kv_heads: int) -> dict:
     """A Mugipel model at a real model's layer sizes: attention layers (the heads of the Qwen3 model of this width,
-    half of each head rotated with rescaled frequencies, scores capped at 50, blocks of 1,024 positions, a learned
+    half of each head rotated with rescaled frequencies, scores capped at 30, blocks of 1,024 positions, a learned
     sink per head) in turn with latent-attention layers (as many heads of 128, a latent of width / 8 numbers per
     token), the last four layers run twice: ``runs`` layer runs in all."""
-    att = {"dim": 128, "heads": heads, "kv_heads": kv_heads, "mask": {"size": 1024}, "scale": 128 ** -0.5, "softcap": 50.0, "vdim": 128,
-           "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 4.0, "fast": 32.0, "original": 8192, "slow": 1.0}}}
+    att = {"dim": 128, "heads": heads, "kv_heads": kv_heads, "mask": {"size": 1024}, "scale": 128 ** -0.5, "softcap": 30.0, "vdim": 128,
+           "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 4.0, "fast": 24.0, "original": 8192, "slow": 2.0}}}
     lat = {"dim": 128, "heads": heads, "kv_rank": max(64, width // 8), "scale": 128 ** -0.5, "vdim": 128}
     stored = runs - 4
     layers = [{"type": "attention" if i % 2 == 0 else "latent_attention", "mixer": dict(att if i % 2 == 0 else lat),
                "mlp": {"ff": ff, "kind": "dense"}} for i in range(stored)]
-    return {"architecture": "Mugipel", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "layers": layers,
+    return {"architecture": "Mugipel", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "residual_mult": 0.6, "layers": layers,
             "loop": {"start": stored - 4, "stop": stored, "times": 2}}
 
 

@@ -39,7 +39,7 @@ def _mugipel(width, vocab, ff, pattern, attention, latent, loop, mult) -> dict:
     ``loop`` = (start, stop, times) or None."""
     layers = [{"type": "attention" if ch == "A" else "latent_attention", "mixer": dict(attention if ch == "A" else latent),
                "mlp": {"kind": "dense", "ff": ff}} for ch in pattern]
-    raw = dict(architecture="Mugipel", width=width, vocab=vocab, norm={"eps": 1e-6}, residual_mult=mult, layers=layers)
+    raw = dict(architecture="Mugipel", width=width, vocab=vocab, norm={"eps": 1e-5}, residual_mult=mult, layers=layers)
     if loop:
         raw["loop"] = dict(zip(("start", "stop", "times"), loop))
     return raw
@@ -50,7 +50,7 @@ PRESETS: dict[str, dict] = {
         96, 503, 160, "ALAL",
         attention={"dim": 32, "heads": 6, "kv_heads": 2, "mask": {"size": 64}, "scale": 32 ** -0.5, "softcap": 30.0, "vdim": 32,
                    "rot": {"base": 10000.0, "dims": 16, "scaling": {"factor": 4.0, "fast": 16.0, "original": 256, "slow": 1.0}}},
-        latent={"dim": 16, "heads": 6, "kv_rank": 48, "scale": 0.25, "vdim": 16}, loop=(2, 4, 2), mult=0.5),
+        latent={"dim": 16, "heads": 6, "kv_rank": 48, "scale": 0.25, "vdim": 16}, loop=(2, 4, 2), mult=0.6),
     "fekulix-tiny": _fekulix(
         96, 503, 160, "PDpd",
         left={"dim": 32, "heads": 6, "kv_heads": 2, "rot": {"base": 10000.0, "dims": 16}, "scale": 32 ** -0.5, "vdim": 16},

@@ -6,7 +6,7 @@ summaries under ``profiles/`` were measured and captured with.
     python -m miniserve_b200.tools.kernel_bench skinny --m 8 --n 4096 --k 1024
     python -m miniserve_b200.tools.kernel_bench sample --batch 8 --top-p 0.9
     python -m miniserve_b200.tools.kernel_bench decay_scan --tokens 2048 --heads 8 --key-dim 64 --value-dim 128 [--delta]
-    python -m miniserve_b200.tools.kernel_bench attn_prefill --tokens 2048 --softcap 50 --chunk 1024 --learned-sink
+    python -m miniserve_b200.tools.kernel_bench attn_prefill --tokens 2048 --softcap 30 --chunk 1024 --learned-sink
     python -m miniserve_b200.tools.kernel_bench add_rmsnorm --m 2048 --n 1024 --offset
     python -m miniserve_b200.tools.kernel_bench pointwise --op channel_gate --tokens 2048 --heads 16 --head-dim 128
 
