@@ -71,6 +71,18 @@ def config_c():
     ], width=56, vocab=83, mult=0.4)
 
 
+def config_d():
+    """Larger and rounder: a width of 288, eight heads in four groups with the whole head of 80 rotated and a smaller
+    value size, a latent of 72 in a head of 80, the latent layer first, the first two layers run three times."""
+    return config([
+        latent_layer(heads=4, dim=32, vdim=96, rank=72, scale=0.2, ff=320),
+        attention_layer(heads=8, kv_heads=4, dim=80, vdim=48, rot=80, base=5000.0, scaling={"factor": 8.0, "fast": 16.0, "original": 128,
+                                                                                           "slow": 2.0}, softcap=15.0, chunk=128, ff=320),
+        attention_layer(heads=4, kv_heads=4, dim=64, vdim=64, rot=32, chunk=96, softcap=None, ff=192),
+        latent_layer(heads=8, dim=48, vdim=32, rank=64, scale=0.15, ff=None),
+    ], width=288, vocab=640, mult=0.5, loop=(0, 2, 3))
+
+
 def tensor_shapes(raw) -> dict[str, tuple]:
     """Names and shapes of a checkpoint of this configuration."""
     w = raw["width"]

@@ -16,7 +16,7 @@ from tests.plain import mugipel_plain as plain
 
 
 # --------------------------------------------------------------------------- configuration
-@pytest.mark.parametrize("make", [mx.config_a, mx.config_b, mx.config_c])
+@pytest.mark.parametrize("make", [mx.config_a, mx.config_b, mx.config_c, mx.config_d])
 def test_declared_tensors_are_the_checkpoint_format(make):
     raw = make()
     _, cfg, spec = resolve(raw)

@@ -350,14 +350,14 @@ def test_parallel_residual_block(dtype, ff):
 
 
 # --------------------------------------------------------------------------- whole models
-@pytest.fixture(scope="module", params=["a", "b", "c"])
+@pytest.fixture(scope="module", params=["a", "b", "c", "d"])
 def model(request, tmp_path_factory):
-    raw = dict(a=mx.config_a, b=mx.config_b, c=mx.config_c)[request.param]()
-    folder = mx.write_model(tmp_path_factory.mktemp("mugipel_" + request.param), raw, seed=dict(a=11, b=12, c=13)[request.param])
+    raw = dict(a=mx.config_a, b=mx.config_b, c=mx.config_c, d=mx.config_d)[request.param]()
+    folder = mx.write_model(tmp_path_factory.mktemp("mugipel_" + request.param), raw, seed=dict(a=11, b=12, c=13, d=14)[request.param])
     # bfloat16: the engine may be as far from the float64 truth as rounding alone takes the oracle (times 2.5: it
     # rounds in more places than the products), and at least 0.1; a lost key or a wrong page costs 0.3 to 1
     noise = mx.rounding_noise(folder, _ids(90, raw["vocab"], 20))
-    return dict(folder=folder, raw=raw, oracle=mx.oracle(folder), page=dict(a=16, b=8, c=32)[request.param],
+    return dict(folder=folder, raw=raw, oracle=mx.oracle(folder), page=dict(a=16, b=8, c=32, d=16)[request.param],
                 tol={"float32": F32, "bfloat16": max(BF16, 2.5 * noise)})
 
 
