@@ -18,9 +18,9 @@
 
 namespace ms {
 
-constexpr int ROWWISE_MAX_D = 256;
+constexpr int ROWWISE_MAX_D = 512;  // a lane holds head_dim / 32 output channels: 8 up to a head size of 256, 16 beyond
 
-template <typename T>
+template <typename T, int DI>
 __global__ void __launch_bounds__(128)
 attention_rowwise_kernel(T* __restrict__ out,            // [T, nq, d]
                          const T* __restrict__ q,        // [T, nq, d]
@@ -52,9 +52,9 @@ attention_rowwise_kernel(T* __restrict__ out,            // [T, nq, d]
   __syncwarp();
 
   float m = -INFINITY, l = 0.f;
-  float acc[ROWWISE_MAX_D / 32];
+  float acc[DI];
 #pragma unroll
-  for (int i = 0; i < ROWWISE_MAX_D / 32; ++i) acc[i] = 0.f;
+  for (int i = 0; i < DI; ++i) acc[i] = 0.f;
 
   for (int tile = (lo >> 5) << 5; tile <= qpos; tile += 32) {
     const int kj = tile + lane;
@@ -84,14 +84,14 @@ attention_rowwise_kernel(T* __restrict__ out,            // [T, nq, d]
     const float p = (s == -INFINITY) ? 0.f : expf(s - m_new);
     l = l * alpha + warp_sum(p);
 #pragma unroll
-    for (int i = 0; i < ROWWISE_MAX_D / 32; ++i) acc[i] *= alpha;
+    for (int i = 0; i < DI; ++i) acc[i] *= alpha;
     const int j_lo = max(lo - tile, 0), j_hi = min(qpos - tile, 31);
     for (int j = j_lo; j <= j_hi; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const unsigned long long bj = __shfl_sync(0xffffffffu, (unsigned long long)base, j);
       const T* vr = v_pool + bj;
 #pragma unroll
-      for (int i = 0; i < ROWWISE_MAX_D / 32; ++i) {
+      for (int i = 0; i < DI; ++i) {
         const int c = lane + 32 * i;
         if (c < d) acc[i] = fmaf(pj, Elem<T>::load(vr + c), acc[i]);
       }
@@ -106,11 +106,11 @@ attention_rowwise_kernel(T* __restrict__ out,            // [T, nq, d]
     const float a = (m == -INFINITY) ? 0.f : expf(m - m_all);
     l = l * a + expf(s0 - m_all);
 #pragma unroll
-    for (int i = 0; i < ROWWISE_MAX_D / 32; ++i) acc[i] *= a;
+    for (int i = 0; i < DI; ++i) acc[i] *= a;
   }
   T* o = out + ((size_t)t * nq + h) * d;
 #pragma unroll
-  for (int i = 0; i < ROWWISE_MAX_D / 32; ++i) {
+  for (int i = 0; i < DI; ++i) {
     const int c = lane + 32 * i;
     if (c < d) Elem<T>::store(o + c, acc[i] / l);
   }
@@ -136,14 +136,17 @@ MS_EXPORT int ms_attention_rowwise(void* out, const void* q, const void* k_pool,
   const long long items = (long long)num_tokens * nq;
   const unsigned blocks = (unsigned)((items + warps - 1) / warps);
   const size_t smem = (size_t)warps * head_dim * sizeof(float);
-  if (dtype == MS_F32)
-    MS_LAUNCH(attention_rowwise_kernel<float>, blocks, warps * 32, smem, stream,
-        (float*)out, (const float*)q, (const float*)k_pool, (const float*)v_pool, positions, row_of_token, page_indptr,
-        page_indices, num_tokens, nq, nkv, head_dim, scale, window, sink, page_shift, num_pages, status, sink_values, softcap, chunk);
-  else
-    MS_LAUNCH(attention_rowwise_kernel<__nv_bfloat16>, blocks, warps * 32, smem, stream,
-        (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
-        positions, row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, head_dim, scale, window, sink, page_shift,
-        num_pages, status, sink_values, softcap, chunk);
+#define MS_ROWWISE_LAUNCH(T, DI)                                                                                        \
+  MS_LAUNCH((attention_rowwise_kernel<T, DI>), blocks, warps * 32, smem, stream, (T*)out, (const T*)q, (const T*)k_pool,  \
+            (const T*)v_pool, positions, row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, head_dim, scale,   \
+            window, sink, page_shift, num_pages, status, sink_values, softcap, chunk)
+  if (dtype == MS_F32) {
+    if (head_dim <= 256) MS_ROWWISE_LAUNCH(float, 8);
+    else MS_ROWWISE_LAUNCH(float, 16);
+  } else {
+    if (head_dim <= 256) MS_ROWWISE_LAUNCH(__nv_bfloat16, 8);
+    else MS_ROWWISE_LAUNCH(__nv_bfloat16, 16);
+  }
+#undef MS_ROWWISE_LAUNCH
   return 0;
 }

@@ -28,7 +28,7 @@ class LatentAttention(Part):
     input_weight = "w_in"  # the attribute that holds the input product's (stacked) matrix; its first ``input_rows`` rows are real
     NAMES = dict(q="q_proj.weight", down="kv_down_proj.weight", norm="kv_norm.weight", up_k="k_up_proj.weight",
                  up_v="v_up_proj.weight", gate="g_proj.weight", o="o_proj.weight")
-    MAX_LATENT = 256  # the largest head size the attention kernels take
+    MAX_LATENT = 512  # the largest head size an attention kernel takes (the tensor-core kernels: 256; beyond, the row-wise kernel)
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

@@ -275,7 +275,8 @@ def _latent_ref(x, w, c):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads, dim, vdim, rank, page", [(3, 16, 24, 40, 8), (5, 12, 20, 36, 16), (2, 40, 40, 128, 16), (1, 64, 8, 16, 4)])
+@pytest.mark.parametrize("heads, dim, vdim, rank, page", [(3, 16, 24, 40, 8), (5, 12, 20, 36, 16), (2, 40, 40, 128, 16), (1, 64, 8, 16, 4),
+                                                          (2, 16, 24, 300, 16)])  # a latent beyond the tensor-core kernels' head sizes
 def test_latent_attention_whole_in_portions_and_decoded(dtype, heads, dim, vdim, rank, page):
     att, c = _latent(dtype, heads, dim, vdim, rank)
     w = _bind(att, dtype)
